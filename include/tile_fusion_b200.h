@@ -1,0 +1,215 @@
+/* C ABI of libtilefusion_b200: fused sparse-dense chains on one B200 (sm_100a).
+ *
+ *   GeMM-SpMM   D = A * (B * C)      A sparse CSR, B and C dense
+ *   SpMM-SpMM   D = A * (B * C)      A and B sparse CSR, C dense
+ *   SDDMM-SpMM  D = (A .* (Q K^T)) * V
+ *
+ * Plain pointers and sizes only.  CSR: int32 row pointers / column indices,
+ * fp32 values, sorted columns.  Dense: row-major fp32.  Every function returns
+ * TF_OK or a negative error code; tf_last_error() gives the message of the
+ * calling thread's last failure.  There is no CPU fallback: executors fail
+ * with TF_ERR_CUDA when no sm_100 device is usable.
+ *
+ * Each entry point names the interface of the reference project
+ * (SwiftWare-Lab/tile-fusion) it stands in for; paths are inside that project.
+ */
+#ifndef TILE_FUSION_B200_H
+#define TILE_FUSION_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  TF_OK = 0,
+  TF_ERR_ARG = -1,         /* null pointer, bad size, unsorted columns, ...           */
+  TF_ERR_UNSUPPORTED = -2, /* a combination the library does not implement             */
+  TF_ERR_CUDA = -3,        /* CUDA runtime error (message holds cudaGetErrorString)    */
+  TF_ERR_TIMEOUT = -4,     /* a bounded in-kernel wait ran out; results are not valid  */
+  TF_ERR_NOMEM = -5
+} tf_status;
+
+const char *tf_last_error(void);
+const char *tf_version(void);
+
+/* ------------------------------------------------------------------------- */
+/* Inspector: reference-format schedule                                       */
+/* ------------------------------------------------------------------------- */
+
+/* Which reference inspector to reproduce bit for bit. */
+typedef enum {
+  /* SparseFusionInspector::generateFusedScheduleForAllFused
+   *   fusion/include/sparse-fusion/Fusion_Inspector.h:32 (fixed tiles) */
+  TF_INSPECT_FIXED = 1,
+  /* InspectorForTileFusedCSRVariableTileSize::generateVariableTileSizeScheduleForBothWavefronts
+   *   Fusion_Inspector.h:676 (SpMM-SpMM, cache budget) */
+  TF_INSPECT_VT_SPMM = 2,
+  /* ...::generateVariableTileSizeScheduleGeMMSpMM  Fusion_Inspector.h:851 */
+  TF_INSPECT_VT_GEMM = 3,
+  /* ...::generateVariableTileSizeSchedule  Fusion_Inspector.h:542 (wave 2 split over threads) */
+  TF_INSPECT_VT_SPMM_THREADS = 4
+} tf_inspect_kind;
+
+/* Mirrors sym_lib::ScheduleParameters (fusion/include/sparse-fusion/Fusion_Defs.h:21-55)
+ * plus the arguments the variable-tile inspectors take. */
+typedef struct {
+  int kind;               /* tf_inspect_kind                                          */
+  int num_threads;        /* _num_threads                                             */
+  int iter_per_partition; /* IterPerPartition (TF_INSPECT_FIXED)                      */
+  int tile_m;             /* TileM: cache budget in bytes (variable-tile kinds)       */
+  int b_cols;             /* BCol: dense width of the first product                   */
+  int c_cols;             /* CCol (TF_INSPECT_VT_GEMM)                                */
+  int data_size;          /* DataSize: bytes per value, 4 for fp32                    */
+} tf_sched_params;
+
+/* The schedule: sym_lib::MultiDimensionalSet
+ *   (fusion/include/sparse-fusion/MultiDimensionalSet.h:15-25), the README's FusedSchedule. */
+typedef struct tf_schedule tf_schedule;
+
+/* Runs one of the reference inspectors on the pattern of A (m x m).
+ * Rejects (TF_ERR_ARG) inputs on which the reference divides by zero or never ends. */
+int tf_inspect(int m, const int *Ap, const int *Ai, const tf_sched_params *p, tf_schedule **out);
+
+/* n1 = levels, n_parts = ptr1[n1], n_ids = ptr2[n_parts], has_ker = ker_begin present. */
+int tf_schedule_dims(const tf_schedule *s, int *n1, int *n_parts, int *n_ids, int *has_ker);
+/* Borrowed pointers into the schedule: ptr1[n1+1], ptr2[n_parts+1], id[n_ids], type[n_ids],
+ * ker_begin[2*n_parts] (NULL when absent).  Any argument may be NULL. */
+int tf_schedule_arrays(const tf_schedule *s, const int **ptr1, const int **ptr2, const int **id,
+                       const int **type, const int **ker_begin);
+/* stats[0..4] = fused rows, fused nnz, tile-size mean, tile-size std, partitions
+ * (the values the reference writes into Stats::OtherStats, Fusion_Inspector.h:671,1013,1049). */
+int tf_schedule_stats(const tf_schedule *s, double stats[5]);
+/* Builds a schedule object from caller arrays (copied), e.g. one produced elsewhere. */
+int tf_schedule_from_arrays(int n1, const int *ptr1, const int *ptr2, const int *id, const int *type,
+                            const int *ker_begin, tf_schedule **out);
+/* Flat int32 image of a schedule, so inspection can be paid once and reused
+ * (the reference keeps the schedule across epochs, FusedGCNModule.py:10). */
+int tf_schedule_serialized_size(const tf_schedule *s, size_t *n_ints);
+int tf_schedule_serialize(const tf_schedule *s, int *buf, size_t n_ints);
+int tf_schedule_deserialize(const int *buf, size_t n_ints, tf_schedule **out);
+void tf_schedule_free(tf_schedule *s);
+
+/* ------------------------------------------------------------------------- */
+/* Device plan                                                                */
+/* ------------------------------------------------------------------------- */
+
+typedef struct {
+  int m, n;          /* rows, columns                                                  */
+  const int *ap;     /* m + 1                                                          */
+  const int *ai;     /* ap[m]                                                          */
+  const float *ax;   /* ap[m]                                                          */
+} tf_csr;            /* host memory */
+
+typedef enum {
+  TF_MODE_STREAM = 0,   /* one persistent launch; the intermediate lives in an L2-sized ring */
+  TF_MODE_SCHEDULE = 1, /* follow a reference-format schedule tile by tile (two waves)       */
+  TF_MODE_UNFUSED = 2   /* two full passes, intermediate through HBM (self-check baseline)   */
+} tf_exec_mode;
+
+typedef struct {
+  int mode;               /* tf_exec_mode                                               */
+  int rows_per_block;     /* rows per work item, 0 = default                            */
+  int ring_bytes;         /* budget for the intermediate ring, 0 = default, <0 = no ring */
+  int slack_blocks;       /* producer lead over consumers in blocks, <0 = default       */
+  int ctas_per_sm;        /* 0 = as many as fit                                         */
+  int halo_rows;          /* rows of the intermediate that arrive from elsewhere and are
+                             appended after the m local rows (multi-GPU); 0 otherwise   */
+  int n_boundary;         /* number of entries of `boundary_rows`                       */
+  const int *boundary_rows; /* local intermediate rows other ranks need first (sorted)  */
+} tf_plan_opts;
+
+typedef struct tf_plan tf_plan;
+
+/* SpMM-SpMM plan for D = A*(B*C); B == NULL means B = A.  `n_cols` = columns of C and D.
+ * `sched` is required for TF_MODE_SCHEDULE and ignored otherwise.
+ * Stands in for the analysis step of the reference's bench classes
+ * (fusion/example/SpMM_SpMM_SP_Demo_Utils.h:165-199). */
+int tf_plan_spmm_spmm(const tf_csr *A, const tf_csr *B, int n_cols, const tf_plan_opts *o,
+                      const tf_schedule *sched, tf_plan **out);
+/* GeMM-SpMM plan for D = A*(B*C), B m x k dense, C k x n_cols dense. */
+int tf_plan_gemm_spmm(const tf_csr *A, int k, int n_cols, const tf_plan_opts *o,
+                      const tf_schedule *sched, tf_plan **out);
+/* SDDMM-SpMM plan: D = (A .* (Q K^T)) V, Q,K m x kq, V m x nv. */
+int tf_plan_sddmm_spmm(const tf_csr *A, int kq, int nv, const tf_plan_opts *o, tf_plan **out);
+void tf_plan_free(tf_plan *p);
+
+/* Host-only preview of the stream plan the library would run (no device needed): `items_out`
+ * receives a malloc'd array of 8 ints per item {kind, block, row_begin, row_end, need, base, aux0,
+ * aux1} in ticket order (release with tf_free); info = {items, producer blocks, consumer blocks,
+ * ring rows, begin of phase 1, begin of phase 2, end, intermediate rows}.  `resident_ctas` is the
+ * number of CTAs assumed resident (it sets the default slack).  No counterpart in the reference. */
+int tf_plan_preview(const tf_csr *A, const tf_csr *B, int producer_is_gemm, int n_cols,
+                    const tf_plan_opts *o, int resident_ctas, int **items_out, long long *n_items,
+                    long long info[8]);
+void tf_free(void *p);
+
+/* info[0] items, [1] producer blocks, [2] consumer blocks, [3] ring rows (0 = full-size
+ * intermediate), [4] grid CTAs, [5] threads per CTA, [6] kernels launched by the last call,
+ * [7] intermediate rows allocated. */
+int tf_plan_info(const tf_plan *p, long long info[8]);
+/* Waits for the plan's work on `stream` and reports TF_ERR_TIMEOUT if a bounded wait ran out. */
+int tf_plan_status(tf_plan *p, void *stream);
+
+/* ------------------------------------------------------------------------- */
+/* Executors, device pointers.  `stream` is a cudaStream_t (NULL = default).   */
+/* D is overwritten.                                                          */
+/* ------------------------------------------------------------------------- */
+
+/* spmmCsrSpmmCsrFusedVectorized2_32SP (fusion/src/SpMM_SpMM_vectorized.cpp:876) and its scalar
+ * form spmmCsrSpmmCsrFused<float> (fusion/src/SpMM_SpMM.cpp:211). */
+int tf_exec_spmm_spmm(tf_plan *p, const float *C, float *D, void *stream);
+
+/* forwardForOneLayerFusedParallelSeparatedVectorizedSP
+ * (fusion/gcn/GCN_Layer_MKL_Forward_Utils.h:218; weight k x n) and, with w_transposed != 0,
+ * the scalar / torch-binding layout weight n x k (ibid. :182; binding-project/src/Functions.cpp:629).
+ * relu != 0 applies max(0, .) to D (binding-project/gcn-e2e-training/FusedGCNModule.py:16). */
+int tf_exec_gemm_spmm(tf_plan *p, const float *B, const float *W, int w_transposed, int relu, float *D,
+                      void *stream);
+
+/* SDDMM as defined by sddmm_cpu (codegen/triton/sddmm.py:173) followed by the CSR SpMM
+ * (fusion/src/SpMM_SpMM.cpp:20); the sampled matrix is never stored. */
+int tf_exec_sddmm_spmm(tf_plan *p, const float *Q, const float *K, const float *V, float *D,
+                       void *stream);
+
+/* Multi-GPU phases of a plan built with boundary_rows / halo_rows:
+ *   phase 0  produce the boundary rows of the intermediate (then send them),
+ *   phase 1  everything that needs no halo row,
+ *   phase 2  the consumer rows that read halo rows (after the receive).
+ * tf_plan_intermediate gives the device buffer: local rows first, then halo rows. */
+int tf_exec_phase(tf_plan *p, int phase, const float *in0, const float *in1, int w_transposed, int relu,
+                  float *D, void *stream);
+int tf_plan_intermediate(tf_plan *p, float **dev_ptr, long long *rows, int *cols);
+/* Device buffers of the halo exchange: `send` holds the boundary rows in the order of
+ * boundary_rows (filled by phase 0), `halo` is where received rows go (the tail of the
+ * intermediate).  No counterpart in the reference, which runs on one shared-memory host. */
+int tf_plan_exchange_buffers(tf_plan *p, float **send, long long *send_rows, float **halo,
+                             long long *halo_rows);
+
+/* ------------------------------------------------------------------------- */
+/* Executors, host pointers: the README-level calls                            */
+/*   swiftware::fusion::spMMSpMMExecutor / geMMSpMMExecutor (README.md:31-32)  */
+/* Copies the dense operands to the device, runs, copies D back.              */
+/* ------------------------------------------------------------------------- */
+int tf_spmm_spmm_host(tf_plan *p, const float *C, float *D);
+int tf_gemm_spmm_host(tf_plan *p, const float *B, const float *W, int w_transposed, int relu, float *D);
+int tf_sddmm_spmm_host(tf_plan *p, const float *Q, const float *K, const float *V, float *D);
+
+/* Plain CSR SpMM  out = A * X  on device pointers (spmmCsrParallel<float>,
+ * fusion/src/SpMM_SpMM.cpp:37, with beta = 0). */
+int tf_spmm_dev(const int *Ap, const int *Ai, const float *Ax, int m, const float *X, int n_cols,
+                float *out, void *stream);
+
+/* Counter-based seeded fills on the device: uniform[-1,1) is bit-identical to the host
+ * generator, N(0, sigma^2) (Box-Muller) agrees with it to float rounding of log/cos;
+ * `offset` is the index of the first element. */
+int tf_fill_uniform(float *dev, long long count, unsigned long long seed, long long offset, void *stream);
+int tf_fill_normal(float *dev, long long count, unsigned long long seed, long long offset, float sigma,
+                   void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TILE_FUSION_B200_H */

@@ -1,0 +1,103 @@
+"""Host logic of the stream planner, checked by emulating the executor's protocol on the CPU."""
+import numpy as np
+import pytest
+
+from tile_fusion_b200 import api, synth
+from tests.emulate import run_items
+
+
+def _csr(t):
+    n = len(t[0]) - 1
+    return api.CSRMatrix(n, n, *t)
+
+
+def _dense_chain(t, C):
+    import scipy.sparse as sp
+    n = len(t[0]) - 1
+    A = sp.csr_matrix((t[2].astype(np.float64), t[1], t[0]), shape=(n, n))
+    return A @ (A @ C.astype(np.float64))
+
+
+@pytest.mark.parametrize("dims,rb,slack,ring_bytes,window", [
+    ((16, 16), 8, 2, 1 << 30, 8),      # ring active
+    ((6, 6, 6), 4, 3, 1 << 30, 12),    # 3-D stencil, ring active
+    ((16, 16), 8, 2, -1, 8),           # ring off
+    ((40,), 4, 1, 1 << 30, 5),
+])
+def test_stream_plan_emulation(built_lib, dims, rb, slack, ring_bytes, window):
+    t = synth.laplacian(dims)
+    A = _csr(t)
+    n, nc = A.M, 3
+    C = synth.uniform(7, (n, nc)).astype(np.float64)
+    items, info = api.plan_preview(A, n_cols=nc, rows_per_block=rb, slack_blocks=slack, ring_bytes=ring_bytes,
+                                   resident_ctas=window)
+    if ring_bytes > 0:
+        assert 0 < info["ring_rows"] < n, info
+    else:
+        assert info["ring_rows"] == 0
+    assert info["items"] == info["producer_blocks"] + info["consumer_blocks"]
+    want = _dense_chain(t, C)
+    for seed in range(3):
+        D, _ = run_items(items, info, t, t, C, nc, n, window=window, seed=seed)
+        np.testing.assert_allclose(D, want, rtol=1e-12, atol=1e-12)
+
+
+def test_stream_plan_random_pattern(built_lib):
+    """Unstructured pattern: windows span everything, so the planner must fall back to a full intermediate."""
+    ap, ai, ax = synth.rmat_gcn(3, 200, 6)
+    A = api.CSRMatrix(200, 200, ap, ai, ax)
+    C = synth.uniform(5, (200, 2)).astype(np.float64)
+    items, info = api.plan_preview(A, n_cols=2, rows_per_block=8, slack_blocks=2, resident_ctas=8)
+    D, _ = run_items(items, info, (ap, ai, ax), (ap, ai, ax), C, 2, 200, window=8, seed=1)
+    np.testing.assert_allclose(D, _dense_chain((ap, ai, ax), C), rtol=1e-10, atol=1e-12)
+
+
+def test_heavy_rows_get_their_own_block(built_lib):
+    n = 300
+    rows = [np.arange(n, dtype=np.int32) if r == 17 else np.array([r], np.int32) for r in range(n)]
+    ap = np.zeros(n + 1, np.int32)
+    ap[1:] = np.cumsum([len(r) for r in rows])
+    ai = np.concatenate(rows)
+    ax = np.ones(len(ai), np.float32)
+    A = api.CSRMatrix(n, n, ap, ai, ax)
+    items, info = api.plan_preview(A, n_cols=4, rows_per_block=8, slack_blocks=1)
+    cons = items[items[:, 0] == 1]
+    blk = cons[(cons[:, 2] <= 17) & (cons[:, 3] > 17)][0]
+    assert blk[3] - blk[2] == 1  # 300 nnz > 8*32: the heavy row stands alone
+    assert cons[:, 3].max() == n and (np.diff(cons[:, 2]) > 0).all()
+
+
+def test_unfused_mode_lists_all_producers_first(built_lib):
+    t = synth.laplacian((12, 12))
+    A = _csr(t)
+    items, info = api.plan_preview(A, n_cols=8, rows_per_block=8, mode=api.MODE_UNFUSED)
+    k = info["producer_blocks"]
+    assert (items[:k, 0] == 0).all() and (items[k:, 0] == 1).all() and info["ring_rows"] == 0
+
+
+def test_halo_plan_defers_halo_consumers(built_lib):
+    """Multi-GPU layout: A is m x (m + halo); consumers that read halo rows go to phase 2."""
+    t = synth.laplacian((8, 8, 4))           # global
+    n = 8 * 8 * 4
+    m, plane = 128, 64                        # this rank owns rows [64, 192): planes 1 and 2
+    r0 = 64
+    ap, ai, ax = t
+    rows = range(r0, r0 + m)
+    cols, vals, ptr = [], [], [0]
+    halo_ids = sorted({int(c) for r in rows for c in ai[ap[r]:ap[r + 1]] if not (r0 <= c < r0 + m)})
+    hmap = {g: m + i for i, g in enumerate(halo_ids)}
+    for r in rows:
+        for p in range(ap[r], ap[r + 1]):
+            c = int(ai[p])
+            cols.append(c - r0 if r0 <= c < r0 + m else hmap[c]); vals.append(ax[p])
+        ptr.append(len(cols))
+    A = api.CSRMatrix(m, m + len(halo_ids), np.array(ptr, np.int32), np.array(cols, np.int32),
+                      np.array(vals, np.float32))
+    boundary = np.array(list(range(0, plane)) + list(range(m - plane, m)), np.int32)
+    items, info = api.plan_preview(A, producer_is_gemm=True, n_cols=4, rows_per_block=16, slack_blocks=1,
+                                   halo_rows=len(halo_ids), boundary_rows=boundary)
+    assert info["ring_rows"] == 0 and info["intermediate_rows"] == m + len(halo_ids)
+    p1 = items[info["phase1_begin"]:info["phase2_begin"]]
+    p2 = items[info["phase2_begin"]:info["end"]]
+    assert (p2[:, 0] == 1).all() and len(p2) == 2 * plane // 16  # first and last plane read halo rows
+    assert (p1[:, 0] == 0).sum() == m // 16 and (p1[:, 0] == 1).sum() == 0  # 2 planes: every consumer touches a halo

@@ -1,0 +1,585 @@
+// C ABI of libtilefusion_b200: plans (device-resident operators + item lists) and executors.
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "kernels.cuh"
+#include "launch.h"
+#include "tf_internal.h"
+
+namespace {
+
+using tf::fail;
+
+#define TF_CUDA(call)                                                                         \
+  do {                                                                                        \
+    cudaError_t e__ = (call);                                                                 \
+    if (e__ != cudaSuccess)                                                                   \
+      return fail(TF_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e__));          \
+  } while (0)
+
+template <class T>
+struct DevBuf {
+  T *p = nullptr;
+  size_t n = 0;
+  ~DevBuf() { if (p) cudaFree(p); }
+  int alloc(size_t count) {
+    if (p) { cudaFree(p); p = nullptr; }
+    n = count;
+    if (count == 0) return TF_OK;
+    cudaError_t e = cudaMalloc(&p, count * sizeof(T));
+    if (e != cudaSuccess) { p = nullptr; return fail(TF_ERR_NOMEM, std::string("cudaMalloc: ") + cudaGetErrorString(e)); }
+    return TF_OK;
+  }
+  int upload(const T *h, size_t count) {
+    int rc = alloc(count);
+    if (rc != TF_OK || count == 0) return rc;
+    TF_CUDA(cudaMemcpy(p, h, count * sizeof(T), cudaMemcpyHostToDevice));
+    return TF_OK;
+  }
+  int upload(const std::vector<T> &v) { return upload(v.data(), v.size()); }
+};
+
+struct DevCsr {
+  int m = 0, n = 0;
+  DevBuf<int> ap, ai;
+  DevBuf<float> ax;
+  int upload(const tf_csr &h) {
+    m = h.m; n = h.n;
+    int rc = ap.upload(h.ap, (size_t)h.m + 1);
+    if (rc == TF_OK) rc = ai.upload(h.ai, (size_t)h.ap[h.m]);
+    if (rc == TF_OK) rc = ax.upload(h.ax, (size_t)h.ap[h.m]);
+    return rc;
+  }
+};
+
+}  // namespace
+
+struct tf_plan {
+  int chain = 0;  // 0 SpMM-SpMM, 1 GeMM-SpMM, 2 SDDMM-SpMM
+  int mode = TF_MODE_STREAM;
+  int m = 0, n_cols = 0, k_dim = 0, halo_rows = 0;
+  int first_cols = 0;  // columns of the first operator (rows of C)
+  DevCsr first, second;
+  bool first_is_second = false;
+  tf::HostPlan hp;
+  DevBuf<int4> items;
+  DevBuf<int> prod_done, cons_done;
+  DevBuf<tfk::ExecState> state;
+  DevBuf<float> inter, sendbuf;
+  // schedule mode
+  DevBuf<int> s_ptr2, s_id, s_type, s_ker;
+  int s_n1 = 0;
+  std::vector<int> s_ptr1;
+  bool s_has_ker = false;
+  // host-pointer path staging
+  DevBuf<float> h_in0, h_in1, h_in2, h_out;
+  int grid = 0, vec = 1, ch = 1;
+  int epoch = 0;
+  int spin_limit = 1 << 22;
+  long long launches = 0;
+  int device = 0;
+};
+
+namespace {
+
+int device_ready(int *sm_count) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(TF_ERR_CUDA, std::string("no usable CUDA device: ") + cudaGetErrorString(e));
+  cudaDeviceProp prop;
+  TF_CUDA(cudaGetDeviceProperties(&prop, dev));
+  if (prop.major < 10) return fail(TF_ERR_CUDA, "this library is built for sm_100a (B200) only");
+  *sm_count = prop.multiProcessorCount;
+  return TF_OK;
+}
+
+int default_rows_per_block(int n_cols, bool gemm) {
+  if (gemm) return 64;
+  return n_cols >= 128 ? 64 : 128;
+}
+
+int upload_items(tf_plan &p) {
+  std::vector<int4> raw(2 * p.hp.items.size());
+  for (size_t i = 0; i < p.hp.items.size(); ++i) {
+    const tf::Item &it = p.hp.items[i];
+    raw[2 * i] = make_int4(it.kind, it.block, it.row_begin, it.row_end);
+    raw[2 * i + 1] = make_int4(it.need, it.base, it.aux0, it.aux1);
+  }
+  return p.items.upload(raw);
+}
+
+int finish_plan(tf_plan &p, const tf_plan_opts &o, int sm_count, bool ring) {
+  const bool a16 = true;  // buffers owned by the plan are 256-byte aligned; callers' pointers are checked per call
+  tfk::choose_shape(p.n_cols, a16, &p.vec, &p.ch);
+  int occ = tfk::stream_occupancy(p.chain, p.vec, p.ch, ring);
+  if (occ <= 0) return fail(TF_ERR_CUDA, "occupancy query failed for the executor kernel");
+  if (o.ctas_per_sm > 0) occ = std::min(occ, o.ctas_per_sm);
+  p.grid = sm_count * occ;
+  return TF_OK;
+}
+
+int zero_state(tf_plan &p) {
+  int rc = p.state.alloc(1);
+  if (rc != TF_OK) return rc;
+  TF_CUDA(cudaMemset(p.state.p, 0, sizeof(tfk::ExecState)));
+  const size_t np = p.hp.prod_rows.empty() ? 0 : p.hp.prod_rows.size() - 1;
+  const size_t nc = p.hp.cons_rows.empty() ? 0 : p.hp.cons_rows.size() - 1;
+  rc = p.prod_done.alloc(std::max<size_t>(np, 1));
+  if (rc == TF_OK) rc = p.cons_done.alloc(std::max<size_t>(nc, 1));
+  if (rc != TF_OK) return rc;
+  TF_CUDA(cudaMemset(p.prod_done.p, 0, p.prod_done.n * sizeof(int)));
+  TF_CUDA(cudaMemset(p.cons_done.p, 0, p.cons_done.n * sizeof(int)));
+  return TF_OK;
+}
+
+int check_opts(const tf_plan_opts *o, tf_plan_opts &out) {
+  std::memset(&out, 0, sizeof(out));
+  out.slack_blocks = -1;
+  if (o) out = *o;
+  if (out.mode < TF_MODE_STREAM || out.mode > TF_MODE_UNFUSED) return fail(TF_ERR_ARG, "plan: unknown mode");
+  if (out.rows_per_block < 0 || out.halo_rows < 0 || out.n_boundary < 0) return fail(TF_ERR_ARG, "plan: negative option");
+  if (out.n_boundary > 0 && !out.boundary_rows) return fail(TF_ERR_ARG, "plan: boundary_rows is null");
+  return TF_OK;
+}
+
+int load_schedule(tf_plan &p, const tf_schedule *s, bool need_ker) {
+  if (!s) return fail(TF_ERR_ARG, "plan: TF_MODE_SCHEDULE needs a schedule");
+  if (need_ker && !s->has_ker) return fail(TF_ERR_ARG, "plan: GeMM-SpMM needs a schedule with ker_begin (separated packing)");
+  for (size_t k = 0; k < s->id.size(); ++k)
+    if (s->id[k] < 0 || s->id[k] >= p.m || (s->type[k] != 0 && s->type[k] != 1))
+      return fail(TF_ERR_ARG, "plan: schedule row id or type out of range");
+  if (need_ker) {
+    const int np = s->ptr1[s->n1];
+    for (int w = 0; w < np; ++w) {
+      const int kb = s->ptr2[w], ke1 = s->ker[2 * w];
+      for (int k = kb; k < ke1; ++k)
+        if (s->type[k] != 0 || s->id[k] != s->id[kb] + (k - kb))
+          return fail(TF_ERR_ARG, "plan: GeMM-SpMM tiles must list consecutive first-loop rows");
+      for (int k = ke1; k < s->ptr2[w + 1]; ++k)
+        if (s->type[k] != 1) return fail(TF_ERR_ARG, "plan: ker_begin does not separate the two loops");
+    }
+  }
+  p.s_n1 = s->n1;
+  p.s_ptr1 = s->ptr1;
+  p.s_has_ker = s->has_ker;
+  int rc = p.s_ptr2.upload(s->ptr2);
+  if (rc == TF_OK) rc = p.s_id.upload(s->id);
+  if (rc == TF_OK) rc = p.s_type.upload(s->type);
+  if (rc == TF_OK && s->has_ker) rc = p.s_ker.upload(s->ker);
+  return rc;
+}
+
+// Common plan construction for the two-operator chains.
+int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int n_cols, const tf_plan_opts *opts,
+                    const tf_schedule *sched, tf_plan **out) {
+  if (!A || !out) return fail(TF_ERR_ARG, "plan: null argument");
+  if (n_cols <= 0) return fail(TF_ERR_ARG, "plan: dense width must be positive");
+  tf_plan_opts o;
+  int rc = check_opts(opts, o);
+  if (rc != TF_OK) return rc;
+  if (A->m <= 0) return fail(TF_ERR_ARG, "plan: matrix must have rows");
+  if ((long long)A->m + o.halo_rows != A->n)
+    return fail(TF_ERR_ARG, "plan: A must be m x (m + halo_rows): its columns index rows of the intermediate");
+  rc = tf::check_csr(A->m, A->n, A->ap, A->ai, false);
+  if (rc != TF_OK) return rc;
+  if (!A->ax) return fail(TF_ERR_ARG, "plan: null value array");
+  const tf_csr *F = chain == 0 ? (B ? B : A) : nullptr;
+  if (F) {
+    if (F->m != A->m) return fail(TF_ERR_ARG, "plan: B must have as many rows as A");
+    if (F != A) {
+      rc = tf::check_csr(F->m, F->n, F->ap, F->ai, false);
+      if (rc != TF_OK) return rc;
+      if (!F->ax) return fail(TF_ERR_ARG, "plan: null value array");
+    }
+    if (o.mode == TF_MODE_SCHEDULE && o.halo_rows) return fail(TF_ERR_UNSUPPORTED, "plan: schedule mode is single-GPU");
+  }
+  if (o.mode != TF_MODE_STREAM && (o.halo_rows || o.n_boundary))
+    return fail(TF_ERR_UNSUPPORTED, "plan: halo exchange is available in stream mode only");
+  int sm_count = 0;
+  rc = device_ready(&sm_count);
+  if (rc != TF_OK) return rc;
+
+  std::unique_ptr<tf_plan> p(new tf_plan());
+  cudaGetDevice(&p->device);
+  p->chain = chain; p->mode = o.mode;
+  p->m = A->m; p->n_cols = n_cols; p->k_dim = k_dim; p->halo_rows = o.halo_rows;
+  rc = p->second.upload(*A);
+  if (rc != TF_OK) return rc;
+  if (F) {
+    p->first_cols = F->n;
+    if (F == A) p->first_is_second = true;
+    else { rc = p->first.upload(*F); if (rc != TF_OK) return rc; }
+  }
+
+  tf::PlanParams pp;
+  pp.m = A->m; pp.n_cols = n_cols;
+  pp.producer_is_gemm = chain == 1;
+  pp.rows_per_block = o.rows_per_block > 0 ? o.rows_per_block : default_rows_per_block(n_cols, chain == 1);
+  pp.max_block_nnz = pp.rows_per_block * 32;
+  pp.halo_rows = o.halo_rows;
+  pp.boundary_rows.assign(o.boundary_rows, o.boundary_rows + o.n_boundary);
+  for (int i = 0; i < o.n_boundary; ++i)
+    if (pp.boundary_rows[i] < 0 || pp.boundary_rows[i] >= A->m || (i && pp.boundary_rows[i] <= pp.boundary_rows[i - 1]))
+      return fail(TF_ERR_ARG, "plan: boundary_rows must be sorted local row ids");
+  pp.ring_bytes = o.mode == TF_MODE_STREAM ? (o.ring_bytes == 0 ? (48LL << 20) : (long long)o.ring_bytes) : -1;
+
+  // grid size first (the default slack depends on how many CTAs are resident); ring-ness does not
+  // change the resource use enough to matter for this estimate
+  rc = finish_plan(*p, o, sm_count, false);
+  if (rc != TF_OK) return rc;
+  pp.max_ctas = p->grid;
+  pp.slack_blocks = o.mode == TF_MODE_UNFUSED ? (1 << 30) : o.slack_blocks;
+  rc = tf::build_stream_plan(pp, F ? F->ap : nullptr, F ? F->ai : nullptr, A->ap, A->ai, p->hp);
+  if (rc != TF_OK) return rc;
+  rc = finish_plan(*p, o, sm_count, p->hp.ring_rows > 0);
+  if (rc != TF_OK) return rc;
+
+  // phase 0 items: boundary rows -> send buffer, in runs of consecutive rows
+  if (!pp.boundary_rows.empty()) {
+    std::vector<tf::Item> pre;
+    size_t i = 0;
+    while (i < pp.boundary_rows.size()) {
+      size_t j = i + 1;
+      while (j < pp.boundary_rows.size() && pp.boundary_rows[j] == pp.boundary_rows[j - 1] + 1 &&
+             (int)(j - i) < pp.rows_per_block)
+        ++j;
+      tf::Item it{};
+      it.kind = 3; it.row_begin = pp.boundary_rows[i]; it.row_end = pp.boundary_rows[i] + (int)(j - i);
+      it.aux0 = (int)i;
+      pre.push_back(it);
+      i = j;
+    }
+    const int shift = (int)pre.size();
+    p->hp.items.insert(p->hp.items.begin(), pre.begin(), pre.end());
+    p->hp.phase_begin[1] += shift; p->hp.phase_begin[2] += shift; p->hp.phase_begin[3] += shift;
+    rc = p->sendbuf.alloc(pp.boundary_rows.size() * (size_t)n_cols);
+    if (rc != TF_OK) return rc;
+  }
+  rc = upload_items(*p);
+  if (rc == TF_OK) rc = zero_state(*p);
+  if (rc == TF_OK) rc = p->inter.alloc((size_t)p->hp.inter_rows * n_cols);
+  if (rc != TF_OK) return rc;
+  if (o.mode == TF_MODE_SCHEDULE) {
+    rc = load_schedule(*p, sched, chain == 1);
+    if (rc != TF_OK) return rc;
+  }
+  *out = p.release();
+  return TF_OK;
+}
+
+tfk::Params base_params(tf_plan &p) {
+  tfk::Params P;
+  std::memset(&P, 0, sizeof(P));
+  const DevCsr &f = p.first_is_second ? p.second : p.first;
+  P.f_ap = f.ap.p; P.f_ai = f.ai.p; P.f_ax = f.ax.p;
+  P.s_ap = p.second.ap.p; P.s_ai = p.second.ai.p; P.s_ax = p.second.ax.p;
+  P.inter = p.inter.p;
+  P.items = p.items.p;
+  P.prod_done = p.prod_done.p; P.cons_done = p.cons_done.p;
+  P.st = p.state.p;
+  P.n_cols = p.n_cols; P.k_dim = p.k_dim; P.m_local = p.m;
+  P.ring_rows = (int)p.hp.ring_rows;
+  P.n_prod = p.hp.prod_rows.empty() ? 0 : (int)p.hp.prod_rows.size() - 1;
+  P.n_cons = p.hp.cons_rows.empty() ? 0 : (int)p.hp.cons_rows.size() - 1;
+  P.spin_limit = p.spin_limit;
+  return P;
+}
+
+bool aligned(const void *q, size_t a) { return (reinterpret_cast<uintptr_t>(q) % a) == 0; }
+
+// vector width usable with the caller's pointers (plan-owned buffers are always aligned)
+void call_shape(const tf_plan &p, std::initializer_list<const void *> ptrs, int *vec, int *ch) {
+  bool a16 = true;
+  for (const void *q : ptrs) a16 = a16 && (!q || aligned(q, 16));
+  tfk::choose_shape(p.n_cols, a16, vec, ch);
+}
+
+int run_phases(tf_plan &p, tfk::Params &P, int first_phase, int last_phase, cudaStream_t s) {
+  int vec, ch;
+  call_shape(p, {P.in0, P.in1, P.in2, P.out}, &vec, &ch);
+  const bool ring = p.hp.ring_rows > 0;
+  if (first_phase <= 1 && last_phase >= 1) ++p.epoch;  // a new pass over the producer blocks
+  P.epoch = p.epoch;
+  p.launches = 0;
+  for (int ph = first_phase; ph <= last_phase; ++ph) {
+    P.item_begin = p.hp.phase_begin[ph];
+    P.item_end = p.hp.phase_begin[ph + 1];
+    if (P.item_end <= P.item_begin) continue;
+    tfk::Params Q = P;
+    if (ph == 0) Q.inter = p.sendbuf.p;
+    Q.reset_wm = (ph == 2) || (ph == 1 && p.hp.phase_begin[3] == p.hp.phase_begin[2] && last_phase >= 1);
+    TF_CUDA(tfk::launch_stream(p.chain, vec, ch, ring, p.grid, Q, s));
+    ++p.launches;
+  }
+  return TF_OK;
+}
+
+int run_unfused(tf_plan &p, tfk::Params &P, cudaStream_t s) {
+  // all producers are listed before all consumers: one launch per half, T through HBM
+  int vec, ch;
+  call_shape(p, {P.in0, P.in1, P.in2, P.out}, &vec, &ch);
+  ++p.epoch;
+  P.epoch = p.epoch;
+  const int np = P.n_prod;
+  p.launches = 0;
+  tfk::Params Q = P;
+  Q.item_begin = 0; Q.item_end = np; Q.reset_wm = 0;
+  TF_CUDA(tfk::launch_stream(p.chain, vec, ch, false, p.grid, Q, s));
+  Q.item_begin = np; Q.item_end = (int)p.hp.items.size(); Q.reset_wm = 1;
+  TF_CUDA(tfk::launch_stream(p.chain, vec, ch, false, p.grid, Q, s));
+  p.launches = 2;
+  return TF_OK;
+}
+
+int run_schedule(tf_plan &p, tfk::Params &P, cudaStream_t s) {
+  int vec, ch;
+  call_shape(p, {P.in0, P.in1, P.in2, P.out}, &vec, &ch);
+  p.launches = 0;
+  for (int l = 0; l < p.s_n1; ++l) {
+    const int nparts = p.s_ptr1[l + 1] - p.s_ptr1[l];
+    if (nparts <= 0) continue;
+    const int grid = std::min(nparts, p.grid);
+    TF_CUDA(tfk::launch_schedule_level(p.chain, vec, ch, grid, P, p.s_ptr2.p, p.s_id.p, p.s_type.p,
+                                       p.s_has_ker ? p.s_ker.p : nullptr, p.s_ptr1[l], p.s_ptr1[l + 1], s));
+    ++p.launches;
+  }
+  return TF_OK;
+}
+
+int run_chain(tf_plan &p, tfk::Params &P, cudaStream_t s) {
+  if (p.mode == TF_MODE_SCHEDULE) return run_schedule(p, P, s);
+  if (p.mode == TF_MODE_UNFUSED) return run_unfused(p, P, s);
+  return run_phases(p, P, 1, 2, s);
+}
+
+int set_device(const tf_plan &p) {
+  TF_CUDA(cudaSetDevice(p.device));
+  return TF_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tf_plan_spmm_spmm(const tf_csr *A, const tf_csr *B, int n_cols, const tf_plan_opts *o,
+                      const tf_schedule *sched, tf_plan **out) {
+  return make_chain_plan(0, A, B, 0, n_cols, o, sched, out);
+}
+
+int tf_plan_gemm_spmm(const tf_csr *A, int k, int n_cols, const tf_plan_opts *o, const tf_schedule *sched,
+                      tf_plan **out) {
+  if (k <= 0) return fail(TF_ERR_ARG, "plan: inner dimension must be positive");
+  return make_chain_plan(1, A, nullptr, k, n_cols, o, sched, out);
+}
+
+int tf_plan_sddmm_spmm(const tf_csr *A, int kq, int nv, const tf_plan_opts *opts, tf_plan **out) {
+  if (!A || !out) return fail(TF_ERR_ARG, "plan: null argument");
+  if (kq <= 0 || nv <= 0) return fail(TF_ERR_ARG, "plan: dense widths must be positive");
+  tf_plan_opts o;
+  int rc = check_opts(opts, o);
+  if (rc != TF_OK) return rc;
+  if (A->m <= 0 || A->n <= 0) return fail(TF_ERR_ARG, "plan: matrix must have rows and columns");
+  rc = tf::check_csr(A->m, A->n, A->ap, A->ai, false);
+  if (rc != TF_OK) return rc;
+  if (!A->ax) return fail(TF_ERR_ARG, "plan: null value array");
+  int sm_count = 0;
+  rc = device_ready(&sm_count);
+  if (rc != TF_OK) return rc;
+  std::unique_ptr<tf_plan> p(new tf_plan());
+  cudaGetDevice(&p->device);
+  p->chain = 2; p->mode = TF_MODE_STREAM;
+  p->m = A->m; p->n_cols = nv; p->k_dim = kq;
+  rc = p->second.upload(*A);
+  if (rc != TF_OK) return rc;
+  p->first_is_second = true;
+  tf::PlanParams pp;
+  pp.m = A->m; pp.n_cols = nv;
+  pp.rows_per_block = o.rows_per_block > 0 ? o.rows_per_block : 32;
+  pp.max_block_nnz = pp.rows_per_block * 32;
+  rc = tf::build_single_pass_plan(pp, A->ap, p->hp);
+  if (rc == TF_OK) rc = finish_plan(*p, o, sm_count, false);
+  if (rc == TF_OK) rc = upload_items(*p);
+  if (rc == TF_OK) rc = zero_state(*p);
+  if (rc != TF_OK) return rc;
+  *out = p.release();
+  return TF_OK;
+}
+
+void tf_plan_free(tf_plan *p) { delete p; }
+
+int tf_plan_info(const tf_plan *p, long long info[8]) {
+  if (!p || !info) return fail(TF_ERR_ARG, "tf_plan_info: null argument");
+  info[0] = (long long)p->hp.items.size();
+  info[1] = p->hp.prod_rows.empty() ? 0 : (long long)p->hp.prod_rows.size() - 1;
+  info[2] = p->hp.cons_rows.empty() ? 0 : (long long)p->hp.cons_rows.size() - 1;
+  info[3] = p->hp.ring_rows;
+  info[4] = p->grid;
+  info[5] = tfk::kThreads;
+  info[6] = p->launches;
+  info[7] = p->hp.inter_rows;
+  return TF_OK;
+}
+
+int tf_plan_status(tf_plan *p, void *stream) {
+  if (!p) return fail(TF_ERR_ARG, "tf_plan_status: null plan");
+  int rc = set_device(*p);
+  if (rc != TF_OK) return rc;
+  TF_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  tfk::ExecState st;
+  TF_CUDA(cudaMemcpy(&st, p->state.p, sizeof(st), cudaMemcpyDeviceToHost));
+  if (st.error) {
+    // leave the plan usable: clear the executor state
+    cudaMemset(p->state.p, 0, sizeof(st));
+    return fail(TF_ERR_TIMEOUT, "a bounded in-kernel wait ran out; the output of the last call is not valid");
+  }
+  return TF_OK;
+}
+
+int tf_exec_spmm_spmm(tf_plan *p, const float *C, float *D, void *stream) {
+  if (!p || !C || !D) return fail(TF_ERR_ARG, "tf_exec_spmm_spmm: null argument");
+  if (p->chain != 0) return fail(TF_ERR_ARG, "tf_exec_spmm_spmm: plan was built for another chain");
+  if (p->halo_rows || p->sendbuf.n) return fail(TF_ERR_ARG, "tf_exec_spmm_spmm: plan has halo rows, drive it with tf_exec_phase");
+  int rc = set_device(*p);
+  if (rc != TF_OK) return rc;
+  tfk::Params P = base_params(*p);
+  P.in0 = C; P.out = D;
+  return run_chain(*p, P, (cudaStream_t)stream);
+}
+
+int tf_exec_gemm_spmm(tf_plan *p, const float *B, const float *W, int w_transposed, int relu, float *D,
+                      void *stream) {
+  if (!p || !B || !W || !D) return fail(TF_ERR_ARG, "tf_exec_gemm_spmm: null argument");
+  if (p->chain != 1) return fail(TF_ERR_ARG, "tf_exec_gemm_spmm: plan was built for another chain");
+  if (p->halo_rows || p->sendbuf.n) return fail(TF_ERR_ARG, "tf_exec_gemm_spmm: plan has halo rows, drive it with tf_exec_phase");
+  int rc = set_device(*p);
+  if (rc != TF_OK) return rc;
+  tfk::Params P = base_params(*p);
+  P.in0 = B; P.in1 = W; P.out = D; P.w_transposed = w_transposed; P.relu = relu;
+  return run_chain(*p, P, (cudaStream_t)stream);
+}
+
+int tf_exec_sddmm_spmm(tf_plan *p, const float *Q, const float *K, const float *V, float *D, void *stream) {
+  if (!p || !Q || !K || !V || !D) return fail(TF_ERR_ARG, "tf_exec_sddmm_spmm: null argument");
+  if (p->chain != 2) return fail(TF_ERR_ARG, "tf_exec_sddmm_spmm: plan was built for another chain");
+  int rc = set_device(*p);
+  if (rc != TF_OK) return rc;
+  tfk::Params P = base_params(*p);
+  P.in0 = Q; P.in1 = K; P.in2 = V; P.out = D;
+  return run_phases(*p, P, 1, 1, (cudaStream_t)stream);
+}
+
+int tf_exec_phase(tf_plan *p, int phase, const float *in0, const float *in1, int w_transposed, int relu,
+                  float *D, void *stream) {
+  if (!p || !in0) return fail(TF_ERR_ARG, "tf_exec_phase: null argument");
+  if (phase < 0 || phase > 2) return fail(TF_ERR_ARG, "tf_exec_phase: phase must be 0, 1 or 2");
+  if (p->chain > 1 || p->mode != TF_MODE_STREAM) return fail(TF_ERR_ARG, "tf_exec_phase: stream-mode chain plans only");
+  if (p->chain == 1 && !in1) return fail(TF_ERR_ARG, "tf_exec_phase: GeMM-SpMM needs the weight");
+  if (phase > 0 && !D) return fail(TF_ERR_ARG, "tf_exec_phase: null output");
+  int rc = set_device(*p);
+  if (rc != TF_OK) return rc;
+  tfk::Params P = base_params(*p);
+  P.in0 = in0; P.in1 = in1; P.out = D; P.w_transposed = w_transposed; P.relu = relu;
+  return run_phases(*p, P, phase, phase, (cudaStream_t)stream);
+}
+
+int tf_plan_intermediate(tf_plan *p, float **dev_ptr, long long *rows, int *cols) {
+  if (!p) return fail(TF_ERR_ARG, "tf_plan_intermediate: null plan");
+  if (dev_ptr) *dev_ptr = p->inter.p;
+  if (rows) *rows = p->hp.inter_rows;
+  if (cols) *cols = p->n_cols;
+  return TF_OK;
+}
+
+int tf_plan_exchange_buffers(tf_plan *p, float **send, long long *send_rows, float **halo, long long *halo_rows) {
+  if (!p) return fail(TF_ERR_ARG, "tf_plan_exchange_buffers: null plan");
+  if (send) *send = p->sendbuf.p;
+  if (send_rows) *send_rows = p->n_cols ? (long long)(p->sendbuf.n / p->n_cols) : 0;
+  if (halo) *halo = p->halo_rows ? p->inter.p + (size_t)(p->hp.inter_rows - p->halo_rows) * p->n_cols : nullptr;
+  if (halo_rows) *halo_rows = p->halo_rows;
+  return TF_OK;
+}
+
+// ---- host-pointer executors -------------------------------------------------
+static int stage_in(DevBuf<float> &buf, const float *h, size_t count, cudaStream_t s) {
+  if (buf.n < count) { int rc = buf.alloc(count); if (rc != TF_OK) return rc; }
+  TF_CUDA(cudaMemcpyAsync(buf.p, h, count * sizeof(float), cudaMemcpyHostToDevice, s));
+  return TF_OK;
+}
+
+static int finish_host(tf_plan *p, float *D, size_t count) {
+  if (p->h_out.n < count) return fail(TF_ERR_ARG, "internal: output staging missing");
+  TF_CUDA(cudaMemcpyAsync(D, p->h_out.p, count * sizeof(float), cudaMemcpyDeviceToHost, 0));
+  return tf_plan_status(p, nullptr);
+}
+
+int tf_spmm_spmm_host(tf_plan *p, const float *C, float *D) {
+  if (!p || !C || !D) return fail(TF_ERR_ARG, "tf_spmm_spmm_host: null argument");
+  if (p->chain != 0) return fail(TF_ERR_ARG, "tf_spmm_spmm_host: plan was built for another chain");
+  int rc = set_device(*p);
+  if (rc != TF_OK) return rc;
+  const size_t nd = (size_t)p->m * p->n_cols;
+  rc = stage_in(p->h_in0, C, (size_t)p->first_cols * p->n_cols, 0);
+  if (rc == TF_OK && p->h_out.n < nd) rc = p->h_out.alloc(nd);
+  if (rc == TF_OK) rc = tf_exec_spmm_spmm(p, p->h_in0.p, p->h_out.p, nullptr);
+  if (rc != TF_OK) return rc;
+  return finish_host(p, D, nd);
+}
+
+int tf_gemm_spmm_host(tf_plan *p, const float *B, const float *W, int w_transposed, int relu, float *D) {
+  if (!p || !B || !W || !D) return fail(TF_ERR_ARG, "tf_gemm_spmm_host: null argument");
+  if (p->chain != 1) return fail(TF_ERR_ARG, "tf_gemm_spmm_host: plan was built for another chain");
+  int rc = set_device(*p);
+  if (rc != TF_OK) return rc;
+  const size_t nd = (size_t)p->m * p->n_cols;
+  rc = stage_in(p->h_in0, B, (size_t)p->m * p->k_dim, 0);
+  if (rc == TF_OK) rc = stage_in(p->h_in1, W, (size_t)p->k_dim * p->n_cols, 0);
+  if (rc == TF_OK && p->h_out.n < nd) rc = p->h_out.alloc(nd);
+  if (rc == TF_OK) rc = tf_exec_gemm_spmm(p, p->h_in0.p, p->h_in1.p, w_transposed, relu, p->h_out.p, nullptr);
+  if (rc != TF_OK) return rc;
+  return finish_host(p, D, nd);
+}
+
+int tf_sddmm_spmm_host(tf_plan *p, const float *Q, const float *K, const float *V, float *D) {
+  if (!p || !Q || !K || !V || !D) return fail(TF_ERR_ARG, "tf_sddmm_spmm_host: null argument");
+  if (p->chain != 2) return fail(TF_ERR_ARG, "tf_sddmm_spmm_host: plan was built for another chain");
+  int rc = set_device(*p);
+  if (rc != TF_OK) return rc;
+  const size_t nd = (size_t)p->m * p->n_cols;
+  rc = stage_in(p->h_in0, Q, (size_t)p->m * p->k_dim, 0);
+  if (rc == TF_OK) rc = stage_in(p->h_in1, K, (size_t)p->second.n * p->k_dim, 0);
+  if (rc == TF_OK) rc = stage_in(p->h_in2, V, (size_t)p->second.n * p->n_cols, 0);
+  if (rc == TF_OK && p->h_out.n < nd) rc = p->h_out.alloc(nd);
+  if (rc == TF_OK) rc = tf_exec_sddmm_spmm(p, p->h_in0.p, p->h_in1.p, p->h_in2.p, p->h_out.p, nullptr);
+  if (rc != TF_OK) return rc;
+  return finish_host(p, D, nd);
+}
+
+int tf_spmm_dev(const int *Ap, const int *Ai, const float *Ax, int m, const float *X, int n_cols, float *out,
+                void *stream) {
+  if (!Ap || !Ai || !Ax || !X || !out) return fail(TF_ERR_ARG, "tf_spmm_dev: null argument");
+  if (m < 0 || n_cols <= 0) return fail(TF_ERR_ARG, "tf_spmm_dev: bad size");
+  int vec, ch;
+  tfk::choose_shape(n_cols, aligned(X, 16) && aligned(out, 16), &vec, &ch);
+  const int grid = std::max(1, std::min((m + tfk::kWarps - 1) / tfk::kWarps, 148 * 8));
+  TF_CUDA(tfk::launch_spmm(vec, ch, grid, Ap, Ai, Ax, m, X, n_cols, out, (cudaStream_t)stream));
+  return TF_OK;
+}
+
+int tf_fill_uniform(float *dev, long long count, unsigned long long seed, long long offset, void *stream) {
+  if (!dev || count < 0) return fail(TF_ERR_ARG, "tf_fill_uniform: bad argument");
+  TF_CUDA(tfk::launch_fill(false, dev, count, seed, offset, 1.f, (cudaStream_t)stream));
+  return TF_OK;
+}
+
+int tf_fill_normal(float *dev, long long count, unsigned long long seed, long long offset, float sigma,
+                   void *stream) {
+  if (!dev || count < 0) return fail(TF_ERR_ARG, "tf_fill_normal: bad argument");
+  TF_CUDA(tfk::launch_fill(true, dev, count, seed, offset, sigma, (cudaStream_t)stream));
+  return TF_OK;
+}
+
+}  // extern "C"

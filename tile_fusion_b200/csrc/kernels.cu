@@ -1,0 +1,411 @@
+// Kernels and launchers of the fused sparse-dense chains (sm_100a).  See kernels.cuh.
+#include <cstdio>
+
+#include "kernels.cuh"
+#include "launch.h"
+
+namespace tfk {
+
+// ---------------------------------------------------------------------------
+// Dense row tile on the CUDA cores: T[rows, :] = B[rows, 0:K] * W  (fp32 FMA, k ascending).
+// 64 x 64 output tile per pass, 16-deep k slices staged in shared memory, 4 x 4 per thread.
+// W is K x N row-major, or N x K when w_transposed.
+// ---------------------------------------------------------------------------
+constexpr int GM = 64, GN = 64, GK = 16;
+
+struct GemmSmem {
+  float a[GK][GM + 4];
+  float b[GK][GN + 4];
+};
+
+// dst_row(r) gives the output row pointer for source row r
+template <class DstRow>
+__device__ __forceinline__ void gemm_rows_cta(const float *__restrict__ B, const float *__restrict__ W,
+                                              bool w_t, int rb, int re, int K, int N, DstRow dst_row,
+                                              GemmSmem &sm) {
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  for (int r0 = rb; r0 < re; r0 += GM) {
+    for (int c0 = 0; c0 < N; c0 += GN) {
+      float acc[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+      for (int k0 = 0; k0 < K; k0 += GK) {
+        // A slice: 64 rows x 16 k; thread loads 4 consecutive k of one row
+        {
+          const int r = tid >> 2, kk = (tid & 3) * 4;
+          const int row = r0 + r;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int k = k0 + kk + u;
+            sm.a[kk + u][r] = (row < re && k < K) ? __ldg(B + (size_t)row * K + k) : 0.f;
+          }
+        }
+        // B slice: 16 k x 64 cols; thread loads 4 consecutive cols of one k
+        {
+          const int kk = tid >> 4, cc = (tid & 15) * 4;
+          const int k = k0 + kk;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int c = c0 + cc + u;
+            float v = 0.f;
+            if (k < K && c < N) v = w_t ? __ldg(W + (size_t)c * K + k) : __ldg(W + (size_t)k * N + c);
+            sm.b[kk][cc + u] = v;
+          }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GK; ++kk) {
+          float av[4], bv[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) av[i] = sm.a[kk][ty * 4 + i];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) bv[j] = sm.b[kk][tx * 4 + j];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = r0 + ty * 4 + i;
+        if (row < re) {
+          float *d = dst_row(row);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int c = c0 + tx * 4 + j;
+            if (c < N) d[c] = acc[i][j];
+          }
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// SDDMM-SpMM row: D[row] = sum_p (ax[p] * <Q[row], K[col_p]>) * V[col_p]
+// ---------------------------------------------------------------------------
+template <int VEC, int CH>
+__device__ __forceinline__ void sddmm_row_warp(const Params &P, int row, int lane) {
+  const int kq = P.k_dim, nv = P.n_cols;
+  const int p0 = __ldg(P.s_ap + row), p1 = __ldg(P.s_ap + row + 1);
+  constexpr int QC = 4;  // Q values kept in registers: kq <= 128
+  float q[QC];
+  const float *qrow = P.in0 + (size_t)row * kq;
+#pragma unroll
+  for (int u = 0; u < QC; ++u) q[u] = (lane + 32 * u < kq) ? __ldg(qrow + lane + 32 * u) : 0.f;
+  constexpr int PANEL = 32 * VEC * CH;
+  for (int col0 = 0; col0 < nv; col0 += PANEL) {
+    float acc[CH][VEC];
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[c][i] = 0.f;
+    for (int p = p0; p < p1; p += 32) {
+      const int cnt = min(32, p1 - p);
+      int col = 0;
+      float val = 0.f;
+      if (lane < cnt) { col = __ldg(P.s_ai + p + lane); val = __ldg(P.s_ax + p + lane); }
+      for (int k = 0; k < cnt; ++k) {
+        const int c = __shfl_sync(kFull, col, k);
+        const float a = __shfl_sync(kFull, val, k);
+        const float *krow = P.in1 + (size_t)c * kq;
+        float part = 0.f;
+#pragma unroll
+        for (int u = 0; u < QC; ++u)
+          if (lane + 32 * u < kq) part = fmaf(q[u], __ldg(krow + lane + 32 * u), part);
+        for (int t = lane + 32 * QC; t < kq; t += 32) part = fmaf(__ldg(qrow + t), __ldg(krow + t), part);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(kFull, part, o);
+        const float s = part * a;
+        const float *vrow = P.in2 + (size_t)c * nv + col0;
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch) {
+          const int cc = (ch * 32 + lane) * VEC;
+          if (col0 + cc < nv) {
+            float x[VEC];
+            load_vec<VEC, false>(x, vrow + cc);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[ch][i] = fmaf(s, x[i], acc[ch][i]);
+          }
+        }
+      }
+    }
+    float *orow = P.out + (size_t)row * nv;
+#pragma unroll
+    for (int ch = 0; ch < CH; ++ch) {
+      const int cc = col0 + (ch * 32 + lane) * VEC;
+      if (cc < nv) store_vec<VEC>(orow + cc, acc[ch], false);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// The persistent executor
+// ---------------------------------------------------------------------------
+constexpr int kHeavyNnz = 64 * kWarps;  // a single-row block at least this heavy is split over the CTA
+
+union StreamSmem {
+  GemmSmem g;
+  float red[kWarps * 32 * 8];  // VEC*CH <= 8
+};
+
+template <int MODE, int VEC, int CH, bool RING>
+__global__ void __launch_bounds__(kThreads) stream_kernel(const Params P) {
+  __shared__ StreamSmem sm;
+  __shared__ int s_next;
+  __shared__ int s_ok;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  ExecState *st = P.st;
+  const int n_items = P.item_end - P.item_begin;
+
+  if (threadIdx.x == 0) s_next = atomicAdd(&st->ticket, 1);
+  __syncthreads();
+  int cur = s_next;
+  while (cur < n_items) {
+    // take the next ticket now and keep it in a register: its latency hides behind this item
+    int nxt = 0;
+    if (threadIdx.x == 0) nxt = atomicAdd(&st->ticket, 1);
+    const int4 ia = __ldg(P.items + 2 * (size_t)(P.item_begin + cur));
+    const int4 ib = __ldg(P.items + 2 * (size_t)(P.item_begin + cur) + 1);
+    const int kind = ia.x, block = ia.y, rb = ia.z, re = ia.w;
+    const int need = ib.x, base = ib.y, send_row = ib.z;
+
+    if (threadIdx.x == 0) {
+      bool ok = true;
+      if (need > 0) ok = wait_for(kind == 1 ? &st->prod_wm : &st->cons_wm, need, st, P.spin_limit);
+      s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) break;
+    // order this CTA's reads of T after the acquire made by thread 0
+    asm volatile("fence.acq_rel.gpu;" ::: "memory");
+
+    if (kind == 0 || kind == 3) {
+      // ---- produce rows [rb, re) of T (kind 3: into the send buffer at row send_row) ----
+      float *dst_base;
+      int ring = 0, pbase = 0;
+      if (kind == 3) dst_base = P.inter + (ptrdiff_t)(send_row - rb) * P.n_cols;  // phase 0: `inter` is the send buffer
+      else { dst_base = P.inter; if (RING) { ring = P.ring_rows; pbase = (rb / ring) * ring; } }
+      auto dst_row = [&](int r) -> float * {
+        int t = r;
+        if (RING && kind == 0) { t = r - pbase; if (t >= ring) t -= ring; }
+        return dst_base + (size_t)t * P.n_cols;
+      };
+      if (MODE == 1) {
+        gemm_rows_cta(P.in0, P.in1, P.w_transposed != 0, rb, re, P.k_dim, P.n_cols, dst_row, sm.g);
+      } else {
+        if (re - rb == 1 && __ldg(P.f_ap + re) - __ldg(P.f_ap + rb) >= kHeavyNnz)
+          spmm_row_cta<VEC, CH, false, false>(P.f_ap, P.f_ai, P.f_ax, rb, P.in0, P.n_cols, dst_row(rb), false,
+                                              0, 0, 0, sm.red);
+        else
+          for (int r = rb + warp; r < re; r += kWarps)
+            spmm_row_warp<VEC, CH, false, false>(P.f_ap, P.f_ai, P.f_ax, r, P.in0, P.n_cols, dst_row(r),
+                                                 false, 0, 0, 0, lane);
+      }
+      if (kind == 0) {
+        __syncthreads();
+        if (threadIdx.x == 0) publish(P.prod_done, &st->prod_wm, block, P.n_prod, P.epoch);
+      }
+    } else if (kind == 1) {
+      // ---- consume: D[rb, re) = A * T ----
+      if (re - rb == 1 && __ldg(P.s_ap + re) - __ldg(P.s_ap + rb) >= kHeavyNnz)
+        spmm_row_cta<VEC, CH, true, RING>(P.s_ap, P.s_ai, P.s_ax, rb, P.inter, P.n_cols,
+                                          P.out + (size_t)rb * P.n_cols, P.relu != 0, base, P.ring_rows,
+                                          P.m_local, sm.red);
+      else
+        for (int r = rb + warp; r < re; r += kWarps)
+          spmm_row_warp<VEC, CH, true, RING>(P.s_ap, P.s_ai, P.s_ax, r, P.inter, P.n_cols,
+                                             P.out + (size_t)r * P.n_cols, P.relu != 0, base, P.ring_rows,
+                                             P.m_local, lane);
+      if (RING) {
+        __syncthreads();
+        if (threadIdx.x == 0) publish(P.cons_done, &st->cons_wm, block, P.n_cons, P.epoch);
+      }
+    } else {
+      // ---- SDDMM-SpMM rows ----
+      for (int r = rb + warp; r < re; r += kWarps) sddmm_row_warp<VEC, CH>(P, r, lane);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_next = nxt;
+    __syncthreads();
+    cur = s_next;
+  }
+  // the last CTA out rewinds the ticket counter (and, after the last phase, the watermarks)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int f = atomicAdd(&st->finished, 1);
+    if (f == (int)gridDim.x - 1) {
+      st->ticket = 0;
+      st->finished = 0;
+      if (P.reset_wm) { st->prod_wm = 0; st->cons_wm = 0; }
+      __threadfence();
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Schedule mode: one CTA per partition of a level of a reference-format schedule.
+//   entries with type 0: produce that row of T; then, after a CTA barrier, entries with type 1:
+//   consume.  Wave 2 partitions hold type-1 entries only.
+// ---------------------------------------------------------------------------
+struct SchedParams {
+  const int *ptr2, *id, *type, *ker;  // device copies; ker may be null
+  int part_begin, part_end;
+};
+
+template <int MODE, int VEC, int CH>
+__global__ void __launch_bounds__(kThreads) schedule_level_kernel(const Params P, const SchedParams S) {
+  __shared__ StreamSmem sm;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int w = S.part_begin + blockIdx.x; w < S.part_end; w += gridDim.x) {
+    const int kb = __ldg(S.ptr2 + w), ke = __ldg(S.ptr2 + w + 1);
+    if (MODE == 1) {
+      // dense producer on the contiguous tile rows [id[kb], id[kb] + ts)
+      const int ke1 = __ldg(S.ker + 2 * w);
+      const int ts = ke1 - kb;
+      if (ts > 0) {
+        const int r0 = __ldg(S.id + kb);
+        auto dst_row = [&](int r) -> float * { return P.inter + (size_t)r * P.n_cols; };
+        gemm_rows_cta(P.in0, P.in1, P.w_transposed != 0, r0, r0 + ts, P.k_dim, P.n_cols, dst_row, sm.g);
+      }
+    } else {
+      for (int k = kb + warp; k < ke; k += kWarps)
+        if (__ldg(S.type + k) == 0) {
+          const int r = __ldg(S.id + k);
+          spmm_row_warp<VEC, CH, false, false>(P.f_ap, P.f_ai, P.f_ax, r, P.in0, P.n_cols,
+                                               P.inter + (size_t)r * P.n_cols, false, 0, 0, 0, lane);
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    for (int k = kb + warp; k < ke; k += kWarps)
+      if (__ldg(S.type + k) == 1) {
+        const int r = __ldg(S.id + k);
+        spmm_row_warp<VEC, CH, true, false>(P.s_ap, P.s_ai, P.s_ax, r, P.inter, P.n_cols,
+                                            P.out + (size_t)r * P.n_cols, P.relu != 0, 0, 0, 0, lane);
+      }
+    __syncthreads();
+  }
+}
+
+// Plain CSR SpMM, one warp per row (out = A * X).
+template <int VEC, int CH>
+__global__ void __launch_bounds__(kThreads) spmm_kernel(const int *ap, const int *ai, const float *ax, int m,
+                                                        const float *x, int n_cols, float *out) {
+  const int lane = threadIdx.x & 31;
+  const int nw = gridDim.x * kWarps;
+  for (int r = blockIdx.x * kWarps + (threadIdx.x >> 5); r < m; r += nw)
+    spmm_row_warp<VEC, CH, false, false>(ap, ai, ax, r, x, n_cols, out + (size_t)r * n_cols, false, 0, 0, 0,
+                                         lane);
+}
+
+// ---------------------------------------------------------------------------
+// Seeded fills: u(seed, idx) = top 24 bits of splitmix64(seed * golden + idx) / 2^24
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
+  unsigned long long z = x + 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+__device__ __forceinline__ float unit24(unsigned long long seed, unsigned long long idx) {
+  return (float)(splitmix64(seed * 0x9E3779B97F4A7C15ull + idx) >> 40) * (1.0f / 16777216.0f);
+}
+__global__ void fill_uniform_kernel(float *p, long long n, unsigned long long seed, long long off) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    p[i] = 2.0f * unit24(seed, (unsigned long long)(off + i)) - 1.0f;
+}
+__global__ void fill_normal_kernel(float *p, long long n, unsigned long long seed, long long off, float sigma) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float u1 = 1.0f - unit24(seed, 2ull * (unsigned long long)(off + i));
+    const float u2 = unit24(seed, 2ull * (unsigned long long)(off + i) + 1ull);
+    p[i] = sigma * sqrtf(-2.0f * logf(u1)) * cosf(6.283185307179586f * u2);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Launchers
+// ---------------------------------------------------------------------------
+typedef void (*StreamFn)(const Params);
+typedef void (*SchedFn)(const Params, const SchedParams);
+
+template <int MODE, int VEC, int CH>
+static StreamFn pick_ring(bool ring) {
+  return ring ? stream_kernel<MODE, VEC, CH, true> : stream_kernel<MODE, VEC, CH, false>;
+}
+template <int MODE>
+static StreamFn pick_stream(int vec, int ch, bool ring) {
+  if (vec == 4) return ch == 2 ? pick_ring<MODE, 4, 2>(ring) : pick_ring<MODE, 4, 1>(ring);
+  if (vec == 2) return ch == 2 ? pick_ring<MODE, 2, 2>(ring) : pick_ring<MODE, 2, 1>(ring);
+  return ch == 2 ? pick_ring<MODE, 1, 2>(ring) : pick_ring<MODE, 1, 1>(ring);
+}
+template <int MODE>
+static SchedFn pick_sched(int vec, int ch) {
+  if (vec == 4) return ch == 2 ? schedule_level_kernel<MODE, 4, 2> : schedule_level_kernel<MODE, 4, 1>;
+  if (vec == 2) return ch == 2 ? schedule_level_kernel<MODE, 2, 2> : schedule_level_kernel<MODE, 2, 1>;
+  return ch == 2 ? schedule_level_kernel<MODE, 1, 2> : schedule_level_kernel<MODE, 1, 1>;
+}
+
+void choose_shape(int n_cols, bool aligned16, int *vec, int *ch) {
+  if (aligned16 && n_cols % 4 == 0 && n_cols > 64) { *vec = 4; *ch = n_cols > 128 ? 2 : 1; }
+  else if (aligned16 && n_cols % 2 == 0) { *vec = 2; *ch = n_cols > 64 ? 2 : 1; }
+  else { *vec = 1; *ch = n_cols > 32 ? 2 : 1; }
+}
+
+static StreamFn stream_fn(int mode, int vec, int ch, bool ring) {
+  switch (mode) {
+    case 0: return pick_stream<0>(vec, ch, ring);
+    case 1: return pick_stream<1>(vec, ch, ring);
+    default: return pick_stream<2>(vec, ch, false);
+  }
+}
+
+int stream_occupancy(int mode, int vec, int ch, bool ring) {
+  int nb = 0;
+  cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, (const void *)stream_fn(mode, vec, ch, ring),
+                                                                kThreads, 0);
+  return e == cudaSuccess ? nb : -1;
+}
+
+cudaError_t launch_stream(int mode, int vec, int ch, bool ring, int grid, const Params &p, cudaStream_t s) {
+  stream_fn(mode, vec, ch, ring)<<<grid, kThreads, 0, s>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_schedule_level(int mode, int vec, int ch, int grid, const Params &p, const int *ptr2,
+                                  const int *id, const int *type, const int *ker, int part_begin, int part_end,
+                                  cudaStream_t s) {
+  if (part_end <= part_begin) return cudaSuccess;
+  SchedParams sp{ptr2, id, type, ker, part_begin, part_end};
+  SchedFn f = mode == 1 ? pick_sched<1>(vec, ch) : pick_sched<0>(vec, ch);
+  f<<<grid, kThreads, 0, s>>>(p, sp);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_spmm(int vec, int ch, int grid, const int *ap, const int *ai, const float *ax, int m,
+                        const float *x, int n_cols, float *out, cudaStream_t s) {
+  if (m <= 0) return cudaSuccess;
+  if (vec == 4) { if (ch == 2) spmm_kernel<4, 2><<<grid, kThreads, 0, s>>>(ap, ai, ax, m, x, n_cols, out);
+                  else spmm_kernel<4, 1><<<grid, kThreads, 0, s>>>(ap, ai, ax, m, x, n_cols, out); }
+  else if (vec == 2) { if (ch == 2) spmm_kernel<2, 2><<<grid, kThreads, 0, s>>>(ap, ai, ax, m, x, n_cols, out);
+                       else spmm_kernel<2, 1><<<grid, kThreads, 0, s>>>(ap, ai, ax, m, x, n_cols, out); }
+  else { if (ch == 2) spmm_kernel<1, 2><<<grid, kThreads, 0, s>>>(ap, ai, ax, m, x, n_cols, out);
+         else spmm_kernel<1, 1><<<grid, kThreads, 0, s>>>(ap, ai, ax, m, x, n_cols, out); }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fill(bool normal, float *p, long long n, unsigned long long seed, long long off, float sigma,
+                        cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  const int grid = (int)std::min<long long>((n + 255) / 256, 148LL * 16);
+  if (normal) fill_normal_kernel<<<grid, 256, 0, s>>>(p, n, seed, off, sigma);
+  else fill_uniform_kernel<<<grid, 256, 0, s>>>(p, n, seed, off);
+  return cudaGetLastError();
+}
+
+}  // namespace tfk

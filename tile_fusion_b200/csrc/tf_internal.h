@@ -1,0 +1,63 @@
+// Internal declarations shared by the host inspector, the planner and the CUDA side.
+#pragma once
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "tile_fusion_b200.h"
+
+struct tf_schedule {
+  int n1 = 0;
+  std::vector<int> ptr1, ptr2, id, type, ker;  // ker empty = absent
+  bool has_ker = false;
+  double stats[5] = {0, 0, 0, 0, 0};
+};
+
+namespace tf {
+
+void set_error(const std::string &msg);
+int fail(int code, const std::string &msg);
+
+// Work item of the persistent executor (two int4 on the device).
+enum ItemKind : int { ITEM_PRODUCE = 0, ITEM_CONSUME = 1, ITEM_SDDMM = 2 };
+struct Item {
+  int kind;       // ItemKind
+  int block;      // index into the producer / consumer done-flag array
+  int row_begin;  // first row of the block
+  int row_end;    // one past the last row
+  int need;       // watermark of the other side this item waits for
+  int base;       // consumer: ring origin of its column window (multiple of ring_rows)
+  int aux0, aux1;
+};
+
+// Host-side execution plan (what the planner derives from the patterns).
+struct HostPlan {
+  std::vector<int> prod_rows;  // producer block boundaries (size blocks + 1)
+  std::vector<int> cons_rows;  // consumer block boundaries
+  std::vector<Item> items;     // all items in ticket order
+  int phase_begin[4] = {0, 0, 0, 0};  // item ranges of the three phases
+  long long ring_rows = 0;     // 0 = intermediate holds every row
+  long long inter_rows = 0;    // rows allocated for the intermediate
+};
+
+struct PlanParams {
+  int m = 0;             // local rows
+  int n_cols = 0;        // dense width of the intermediate
+  int rows_per_block = 0;
+  long long ring_bytes = 0;
+  int slack_blocks = -1;
+  int max_ctas = 0;      // CTAs that will be resident (for the default slack)
+  bool producer_is_gemm = false;
+  int halo_rows = 0;
+  std::vector<int> boundary_rows;
+  int max_block_nnz = 0;
+};
+
+// first: CSR pattern of the first operator (nullptr for a dense producer); second: of A.
+int build_stream_plan(const PlanParams &pp, const int *first_ap, const int *first_ai, const int *sec_ap,
+                      const int *sec_ai, HostPlan &out);
+int build_single_pass_plan(const PlanParams &pp, const int *ap, HostPlan &out);
+
+int check_csr(int m, int ncols, const int *ap, const int *ai, bool need_sorted);
+
+}  // namespace tf
