@@ -150,6 +150,10 @@ void tf_free(void *p);
  * intermediate), [4] grid CTAs, [5] threads per CTA, [6] kernels launched by the last call,
  * [7] intermediate rows allocated. */
 int tf_plan_info(const tf_plan *p, long long info[8]);
+/* Number of polls (each followed by a short sleep) after which an in-kernel wait on another
+ * block's completion gives up, sets the plan's error status and lets the kernel return.
+ * Default 1 << 22 (of the order of a second). */
+int tf_plan_set_wait_limit(tf_plan *p, int polls);
 /* Waits for the plan's work on `stream` and reports TF_ERR_TIMEOUT if a bounded wait ran out. */
 int tf_plan_status(tf_plan *p, void *stream);
 

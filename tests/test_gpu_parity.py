@@ -1,0 +1,279 @@
+"""Parity of the CUDA executors (through the C ABI) with the CPU oracle and the golden vectors.
+Tolerance: rel-L2 <= 1e-5 and max-abs <= 1e-4 * ||D||_inf (tests/common.py)."""
+import numpy as np
+import pytest
+
+from tests import common
+from tile_fusion_b200 import api, synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch_cuda(built_lib):
+    import torch
+    torch.cuda.init()
+    return torch
+
+
+def _csr(t):
+    n = len(t[0]) - 1
+    return api.CSRMatrix(n, n, *t)
+
+
+def _dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _sched(A, kind, n_cols, k=0, threads=4):
+    if kind == 1:
+        return api.inspector(A, threads, kind=1, iter_per_partition=max(8, A.M // 37))
+    if kind == 2:
+        return api.inspector(A, threads, kind=2, tile_m=40 * 4 * n_cols * 3, b_cols=n_cols)
+    return api.inspector(A, threads, kind=3, tile_m=4 * (k * n_cols + 120 * (k + n_cols)), b_cols=k, c_cols=n_cols)
+
+
+MATS = {
+    "lap2d_40x33": ("lap", (40, 33)),
+    "lap3d_14": ("lap", (14, 14, 14)),
+    "lap1d_3000": ("lap", (3000,)),
+    "rmat_3000": ("rmat_gcn", 7, 3000, 14),
+}
+
+
+@pytest.mark.parametrize("n_cols", [128, 64, 47, 100, 256, 8, 300])
+def test_spmm_kernel(torch_cuda, oracle, n_cols):
+    torch = torch_cuda
+    from tile_fusion_b200 import _lib
+    a = common.matrix(MATS["rmat_3000"])
+    x = synth.uniform(5, (3000, n_cols))
+    want = oracle.spmm(a[0], a[1], a[2], x)
+    out = torch.empty((3000, n_cols), device="cuda")
+    ap, ai, ax, xd = (_dev(torch, v) for v in (a[0], a[1], a[2], x))
+    _lib.check(_lib.lib().tf_spmm_dev(ap.data_ptr(), ai.data_ptr(), ax.data_ptr(), 3000, xd.data_ptr(), n_cols,
+                                      out.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    common.assert_close(out.cpu().numpy(), want, f"spmm N={n_cols}")
+
+
+@pytest.mark.parametrize("mat", list(MATS))
+@pytest.mark.parametrize("n_cols", [128, 32, 47])
+def test_spmm_spmm_all_modes(torch_cuda, oracle, mat, n_cols):
+    torch = torch_cuda
+    a = common.matrix(MATS[mat])
+    A = _csr(a)
+    c = synth.uniform(3, (A.M, n_cols))
+    want, _ = oracle.spmm_spmm(a, a, c, oracle.inspect_fixed(a[0], a[1], 2, 64))
+    cd = _dev(torch, c)
+    results = {}
+    variants = [("stream_ring", dict(mode=api.MODE_STREAM, rows_per_block=16, slack_blocks=4, ring_bytes=1 << 30)),
+                ("stream_default", dict(mode=api.MODE_STREAM)),
+                ("stream_noring", dict(mode=api.MODE_STREAM, ring_bytes=-1, rows_per_block=8)),
+                ("unfused", dict(mode=api.MODE_UNFUSED)),
+                ("sched_fixed", dict(mode=api.MODE_SCHEDULE, schedule=_sched(A, 1, n_cols))),
+                ("sched_vt", dict(mode=api.MODE_SCHEDULE, schedule=_sched(A, 2, n_cols)))]
+    for name, kw in variants:
+        plan = api.Plan("spmm_spmm", A, n_cols=n_cols, **kw)
+        d = torch.full((A.M, n_cols), float("nan"), device="cuda")
+        for _ in range(2):  # twice: the executor state must rewind
+            plan.spmm_spmm(cd, d)
+        plan.status()
+        results[name] = d.cpu().numpy()
+        common.assert_close(results[name], want, f"{mat} N={n_cols} {name}")
+        if name == "stream_ring" and mat.startswith("lap"):
+            assert 0 < plan.info()["ring_rows"] < A.M
+        plan.close()
+    # every mode adds the same products in the same order
+    for name in results:
+        np.testing.assert_array_equal(results[name], results["unfused"], err_msg=name)
+
+
+def test_spmm_spmm_two_operators_and_host_path(torch_cuda, oracle):
+    a = common.matrix(MATS["lap2d_40x33"])
+    b = common.matrix(("rmat_gcn", 3, 40 * 33, 5))
+    A, B = _csr(a), _csr(b)
+    c = synth.uniform(3, (A.M, 64))
+    want, _ = oracle.spmm_spmm(a, b, c, oracle.inspect_fixed(a[0], a[1], 2, 64))
+    d = np.zeros((A.M, 64), np.float32)
+    api.spMMSpMMExecutor(A, B, api.Matrix(A.M, 64, c), api.Matrix(A.M, 64, d), None, 8)
+    common.assert_close(d, want, "host path, A != B")
+    s = api.inspector(A, 4, kind=2, tile_m=60000, b_cols=64)
+    d2 = np.zeros_like(d)
+    api.spMMSpMMExecutor(A, A, api.Matrix(A.M, 64, c), api.Matrix(A.M, 64, d2), s, 8, mode=api.MODE_SCHEDULE)
+    want2, _ = oracle.spmm_spmm(a, a, c, oracle.inspect_variable(2, a[0], a[1], 4, 60000, 64))
+    common.assert_close(d2, want2, "host path, schedule mode")
+
+
+@pytest.mark.parametrize("mat", ["lap2d_40x33", "rmat_3000"])
+@pytest.mark.parametrize("k,n_cols", [(64, 64), (100, 256), (256, 47), (17, 33)])
+def test_gemm_spmm_all_modes(torch_cuda, oracle, mat, k, n_cols):
+    torch = torch_cuda
+    a = common.matrix(MATS[mat])
+    A = _csr(a)
+    b = synth.uniform(2, (A.M, k))
+    w = synth.uniform(3, (k, n_cols))
+    so = oracle.inspect_fixed(a[0], a[1], 2, 64)
+    want, _ = oracle.gemm_spmm(a, b, w, so)
+    bd, wd, wtd = _dev(torch, b), _dev(torch, w), _dev(torch, w.T)
+    for name, kw in [("stream", dict(mode=api.MODE_STREAM)),
+                     ("stream_small", dict(mode=api.MODE_STREAM, rows_per_block=16, slack_blocks=3)),
+                     ("unfused", dict(mode=api.MODE_UNFUSED)),
+                     ("sched_fixed", dict(mode=api.MODE_SCHEDULE, schedule=_sched(A, 1, n_cols))),
+                     ("sched_vt", dict(mode=api.MODE_SCHEDULE, schedule=_sched(A, 3, n_cols, k)))]:
+        plan = api.Plan("gemm_spmm", A, k=k, n_cols=n_cols, **kw)
+        d = torch.full((A.M, n_cols), float("nan"), device="cuda")
+        plan.gemm_spmm(bd, wd, d)
+        plan.status()
+        common.assert_close(d.cpu().numpy(), want, f"{mat} {k}x{n_cols} {name}")
+        d.fill_(float("nan"))
+        plan.gemm_spmm(bd, wtd, d, w_transposed=True, relu=True)
+        plan.status()
+        common.assert_close(d.cpu().numpy(), np.maximum(want, 0), f"{mat} {k}x{n_cols} {name} transposed+relu")
+        plan.close()
+
+
+def test_gemm_spmm_host_executor(torch_cuda, oracle):
+    a = common.matrix(MATS["lap3d_14"])
+    A = _csr(a)
+    b, w = synth.uniform(2, (A.M, 48)), synth.uniform(3, (48, 96))
+    want, _ = oracle.gemm_spmm(a, b, w, oracle.inspect_fixed(a[0], a[1], 2, 64))
+    d = np.zeros((A.M, 96), np.float32)
+    api.geMMSpMMExecutor(A, api.Matrix(A.M, 48, b), api.Matrix(48, 96, w), api.Matrix(A.M, 96, d), None, 4)
+    common.assert_close(d, want, "geMMSpMMExecutor host")
+
+
+@pytest.mark.parametrize("kq,nv", [(64, 128), (32, 64), (100, 47), (160, 256)])
+def test_sddmm_spmm(torch_cuda, oracle, kq, nv):
+    torch = torch_cuda
+    a = synth.rmat_pattern(4, 2500, 20)
+    A = api.CSRMatrix(2500, 2500, *a)
+    q, k, v = synth.normal(2, (2500, kq), 0.125), synth.normal(3, (2500, kq), 0.125), synth.normal(4, (2500, nv), 0.125)
+    want = oracle.sddmm_spmm(a, q, k, v)
+    d = torch.full((2500, nv), float("nan"), device="cuda")
+    api.sddmmSpMMExecutor(A, api.Matrix(2500, kq, _dev(torch, q)), api.Matrix(2500, kq, _dev(torch, k)),
+                          api.Matrix(2500, nv, _dev(torch, v)), api.Matrix(2500, nv, d))
+    torch.cuda.synchronize()
+    common.assert_close(d.cpu().numpy(), want, f"SDDMM-SpMM {kq}/{nv}")
+    dh = np.zeros((2500, nv), np.float32)
+    api.sddmmSpMMExecutor(A, api.Matrix(2500, kq, q), api.Matrix(2500, kq, k), api.Matrix(2500, nv, v),
+                          api.Matrix(2500, nv, dh))
+    np.testing.assert_array_equal(dh, d.cpu().numpy())
+
+
+def test_gcn_two_layers(torch_cuda, oracle):
+    torch = torch_cuda
+    g = synth.rmat_gcn(6, 4000, 25)
+    A = api.CSRMatrix(4000, 4000, *g)
+    x, w1, w2 = synth.normal(2, (4000, 100)), synth.glorot(3, 256, 100), synth.glorot(4, 47, 256)
+    out, plans = api.gcn_forward(A, _dev(torch, x), _dev(torch, w1), _dev(torch, w2))
+    torch.cuda.synchronize()
+    common.assert_close(out.cpu().numpy(), oracle.gcn2(g, x, w1, w2), "2-layer GCN")
+
+
+@pytest.mark.parametrize("name", [k for k, v in common.manifest().items() if "chain" in v])
+def test_golden_outputs(torch_cuda, name):
+    """Outputs of the unmodified reference on seeded inputs (tests/golden)."""
+    torch = torch_cuda
+    case = common.manifest()[name]
+    a = common.matrix(case["matrix"])
+    A = _csr(a)
+    prm = case["params"]
+    s = api.inspector(A, prm["threads"], kind=case["kind"], iter_per_partition=prm.get("iter_per_part", 1),
+                      tile_m=prm.get("tile_m", 1), b_cols=prm.get("bcol", 1), c_cols=prm.get("ccol", 1))
+    want = common.golden(name)["D"]
+    for mode in (api.MODE_STREAM, api.MODE_SCHEDULE):
+        d = np.zeros_like(want)
+        if case["chain"] == "spmm_spmm":
+            c = synth.uniform(3, (A.M, case["dims"]["n"]))
+            api.spMMSpMMExecutor(A, A, api.Matrix(*c.shape, c), api.Matrix(*d.shape, d), s, 2, mode=mode)
+        else:
+            b = synth.uniform(2, (A.M, case["dims"]["k"]))
+            w = synth.uniform(3, (case["dims"]["k"], case["dims"]["n"]))
+            api.geMMSpMMExecutor(A, api.Matrix(*b.shape, b), api.Matrix(*w.shape, w), api.Matrix(*d.shape, d), s, 2,
+                                 mode=mode)
+        common.assert_close(d, want, f"{name} mode {mode}")
+
+
+def test_device_fills_match_host_generators(torch_cuda):
+    torch = torch_cuda
+    from tile_fusion_b200 import _lib
+    n = 100003
+    t = torch.empty(n, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(_lib.lib().tf_fill_uniform(t.data_ptr(), n, 3, 1000, st))
+    np.testing.assert_array_equal(t.cpu().numpy(), synth.uniform(3, (n,), start=1000))
+    _lib.check(_lib.lib().tf_fill_normal(t.data_ptr(), n, 4, 77, 0.125, st))
+    np.testing.assert_allclose(t.cpu().numpy(), synth.normal(4, (n,), 0.125, start=77), rtol=2e-5, atol=1e-6)
+
+
+def test_edge_shapes(torch_cuda, oracle):
+    torch = torch_cuda
+    # one row, one column; empty rows; N = 1
+    ap = np.array([0, 1], np.int32)
+    A = api.CSRMatrix(1, 1, ap, np.array([0], np.int32), np.array([2.0], np.float32))
+    d = np.zeros((1, 1), np.float32)
+    api.spMMSpMMExecutor(A, A, api.Matrix(1, 1, np.array([[3.0]], np.float32)), api.Matrix(1, 1, d), None)
+    assert d[0, 0] == 12.0
+    n = 257
+    rows = [np.array([], np.int32) if r % 5 == 0 else np.array(sorted({r, (r * 7) % n, n - 1 - r}), np.int32)
+            for r in range(n)]
+    ap = np.zeros(n + 1, np.int32)
+    ap[1:] = np.cumsum([len(r) for r in rows])
+    ai = np.concatenate(rows).astype(np.int32)
+    ax = synth.uniform(9, (len(ai),))
+    t = (ap, ai, ax)
+    A = api.CSRMatrix(n, n, *t)
+    c = synth.uniform(3, (n, 5))
+    want = oracle.spmm(ap, ai, ax, oracle.spmm(ap, ai, ax, c))
+    d = np.full((n, 5), np.nan, np.float32)
+    api.spMMSpMMExecutor(A, A, api.Matrix(n, 5, c), api.Matrix(n, 5, d), None)
+    common.assert_close(d, want, "empty rows")
+    with pytest.raises(ValueError):
+        api.spMMSpMMExecutor(A, A, api.Matrix(n, 5, c), api.Matrix(n, 4, np.zeros((n, 4), np.float32)), None)
+    with pytest.raises(api.TileFusionError):
+        api.Plan("gemm_spmm", A, k=0, n_cols=4)
+
+
+def test_heavy_row_split_over_cta(torch_cuda, oracle):
+    """A row far above the per-block nonzero cap is reduced by the whole CTA."""
+    torch = torch_cuda
+    n = 4096
+    rows = [np.arange(n, dtype=np.int32) if r in (5, 4000) else np.array([r], np.int32) for r in range(n)]
+    ap = np.zeros(n + 1, np.int32)
+    ap[1:] = np.cumsum([len(r) for r in rows])
+    ai = np.concatenate(rows)
+    ax = synth.uniform(8, (len(ai),))
+    A = api.CSRMatrix(n, n, ap, ai, ax)
+    c = synth.uniform(3, (n, 128))
+    want = oracle.spmm(ap, ai, ax, oracle.spmm(ap, ai, ax, c))
+    d = np.zeros((n, 128), np.float32)
+    api.spMMSpMMExecutor(A, A, api.Matrix(n, 128, c), api.Matrix(n, 128, d), None)
+    common.assert_close(d, want, "heavy rows")
+
+
+def test_bounded_wait_reports_timeout(torch_cuda):
+    """Failure detection without a GPU fault: consumers of a halo plan are launched without the
+    producers they wait for; the wait runs out, the kernel returns and the host reads the status."""
+    torch = torch_cuda
+    a = synth.laplacian((8, 8, 4))
+    m, halo = 256, 0
+    # a plan with a (fake) halo: columns of the last rows point to 4 extra rows
+    ap, ai, ax = a
+    ai2 = ai.copy()
+    ai2[-3:] = [m, m + 1, m + 3]
+    A = api.CSRMatrix(m, m + 4, ap, ai2, ax)
+    plan = api.Plan("spmm_spmm", A, B=api.CSRMatrix(m, m, *a), n_cols=32, halo_rows=4,
+                    boundary_rows=np.array([0, 1], np.int32))
+    plan.set_wait_limit(200)
+    c = torch.zeros((m, 32), device="cuda")
+    d = torch.zeros((m, 32), device="cuda")
+    plan.phase(2, c, None, d)  # phase 1 never ran: nothing publishes the producer blocks
+    with pytest.raises(api.TileFusionError) as e:
+        plan.status()
+    assert e.value.code == -4
+    # the plan stays usable
+    plan.set_wait_limit(1 << 22)
+    plan.phase(0, c, None, None)
+    plan.phase(1, c, None, d)
+    plan.phase(2, c, None, d)
+    plan.status()
+    assert float(d.abs().sum()) == 0.0

@@ -1,0 +1,99 @@
+"""Host logic of the row-block partition, and the halo exchange choreography over gloo (2 ranks)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from tile_fusion_b200 import partition, synth
+
+
+def test_bounds_and_layouts_are_consistent():
+    dims = (6, 5, 8)
+    n = 240
+    full = synth.laplacian(dims)
+    for world in (1, 2, 3, 4):
+        bounds = partition.row_bounds(None, n, world)
+        assert bounds[0] == 0 and bounds[-1] == n and (np.diff(bounds) >= n // world).all()
+        rows = [synth.laplacian_rows(dims, int(bounds[g]), int(bounds[g + 1])) for g in range(world)]
+        assert np.array_equal(np.concatenate([r[1] for r in rows]), full[1])
+        assert np.array_equal(np.concatenate([r[2] for r in rows]), full[2])
+        halos = [partition.halo_of(rows[g][1], int(bounds[g]), int(bounds[g + 1])) for g in range(world)]
+        lays = [partition.make_layout(g, bounds, halos) for g in range(world)]
+        for g, lay in enumerate(lays):
+            assert sum(s.count for s in lay.recv) == len(lay.halo_ids)
+            for s in lay.recv:  # what g receives from p is what p sends to g, in the same order
+                t = next(x for x in lays[s.peer].send if x.peer == g)
+                assert t.count == s.count
+                sent_local = lays[s.peer].boundary_rows[t.start:t.start + t.count] if t.index is None \
+                    else lays[s.peer].boundary_rows[t.index]
+                np.testing.assert_array_equal(sent_local + bounds[s.peer], lay.halo_ids[s.start:s.start + s.count])
+            loc = partition.localize_columns(rows[g][1], lay)
+            assert loc.min() >= 0 and loc.max() < lay.m + len(lay.halo_ids)
+            hid = np.concatenate([lay.halo_ids, [-1]])  # world 1: no halo
+            back = np.where(loc < lay.m, loc + lay.r0, hid[np.clip(loc - lay.m, 0, len(hid) - 1)])
+            np.testing.assert_array_equal(back, rows[g][1])
+
+
+def test_nnz_balanced_bounds():
+    ap, ai, ax = synth.rmat_gcn(3, 4000, 10)
+    b = partition.row_bounds(ap, 4000, 4, by="nnz")
+    per = np.diff(ap[b])
+    assert per.sum() == ap[-1] and per.max() < 1.5 * per.mean()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_main(rank, world, port, dims, nc, ret):
+    import torch
+    import torch.distributed as dist
+    import scipy.sparse as sp
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n = int(np.prod(dims))
+        bounds = partition.row_bounds(None, n, world)
+        r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
+        ap, ai, ax = synth.laplacian_rows(dims, r0, r1)
+        mine = partition.halo_of(ai, r0, r1)
+        halos = [None] * world
+        dist.all_gather_object(halos, mine)
+        lay = partition.make_layout(rank, bounds, halos)
+        # numpy stands in for the device kernels: T rows of this rank = B_local @ W
+        b = synth.uniform(2, (n, 8))[r0:r1].astype(np.float64)
+        w = synth.uniform(3, (8, nc)).astype(np.float64)
+        t_local = b @ w
+        send = torch.from_numpy(t_local[lay.boundary_rows])            # phase 0
+        halo = torch.zeros((len(lay.halo_ids), nc), dtype=torch.float64)
+        ops = [dist.P2POp(dist.isend, send[s.start:s.start + s.count].contiguous(), s.peer) for s in lay.send]
+        ops += [dist.P2POp(dist.irecv, halo[s.start:s.start + s.count], s.peer) for s in lay.recv]
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+        t_all = np.concatenate([t_local, halo.numpy()])               # local rows, then halo rows
+        a_loc = sp.csr_matrix((ax.astype(np.float64), partition.localize_columns(ai, lay), ap),
+                              shape=(lay.m, lay.m + len(lay.halo_ids)))
+        ret[rank] = (r0, a_loc @ t_all)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_halo_exchange_two_ranks_gloo():
+    import torch.multiprocessing as mp
+    import scipy.sparse as sp
+    dims, nc, world = (5, 4, 6), 3, 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = _free_port()
+    mp.spawn(_rank_main, args=(world, port, dims, nc, ret), nprocs=world, join=True)
+    a = synth.laplacian(dims)
+    n = int(np.prod(dims))
+    A = sp.csr_matrix((a[2].astype(np.float64), a[1], a[0]), shape=(n, n))
+    want = A @ (synth.uniform(2, (n, 8)).astype(np.float64) @ synth.uniform(3, (8, nc)).astype(np.float64))
+    got = np.concatenate([ret[g][1] for g in range(world)])
+    np.testing.assert_allclose(got, want, rtol=1e-12, atol=1e-12)

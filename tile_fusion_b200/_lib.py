@@ -41,7 +41,7 @@ EXPORTS = [
     "tf_schedule_free", "tf_plan_spmm_spmm", "tf_plan_gemm_spmm", "tf_plan_sddmm_spmm", "tf_plan_free",
     "tf_plan_info", "tf_plan_status", "tf_exec_spmm_spmm", "tf_exec_gemm_spmm", "tf_exec_sddmm_spmm",
     "tf_exec_phase", "tf_plan_intermediate", "tf_plan_exchange_buffers", "tf_spmm_spmm_host", "tf_gemm_spmm_host",
-    "tf_sddmm_spmm_host", "tf_spmm_dev", "tf_fill_uniform", "tf_fill_normal", "tf_plan_preview", "tf_free",
+    "tf_sddmm_spmm_host", "tf_spmm_dev", "tf_fill_uniform", "tf_fill_normal", "tf_plan_preview", "tf_free", "tf_plan_set_wait_limit",
 ]
 
 _lib = None
@@ -92,6 +92,7 @@ def lib() -> C.CDLL:
     L.tf_plan_preview.argtypes = [C.POINTER(Csr), C.POINTER(Csr), i, i, C.POINTER(PlanOpts), i, C.POINTER(vp),
                                   C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]
     L.tf_free.argtypes = [vp]
+    L.tf_plan_set_wait_limit.argtypes = [vp, i]
     L.tf_free.restype = None
     _lib = L
     return L

@@ -221,6 +221,9 @@ class Plan:
         """Waits for the plan's work and raises if a bounded in-kernel wait ran out."""
         check(_lib.lib().tf_plan_status(self._h, stream if stream is not None else _stream_ptr()))
 
+    def set_wait_limit(self, polls: int) -> None:
+        check(_lib.lib().tf_plan_set_wait_limit(self._h, int(polls)))
+
     def exchange_buffers(self):
         """(send_ptr, send_rows, halo_ptr, halo_rows) of the halo exchange."""
         sp, hp = C.c_void_p(), C.c_void_p()

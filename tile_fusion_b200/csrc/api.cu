@@ -263,6 +263,7 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
   if (rc == TF_OK) rc = zero_state(*p);
   if (rc == TF_OK) rc = p->inter.alloc((size_t)p->hp.inter_rows * n_cols);
   if (rc != TF_OK) return rc;
+  TF_CUDA(cudaMemset(p->inter.p, 0, p->inter.n * sizeof(float)));
   if (o.mode == TF_MODE_SCHEDULE) {
     rc = load_schedule(*p, sched, chain == 1);
     if (rc != TF_OK) return rc;
@@ -421,6 +422,12 @@ int tf_plan_info(const tf_plan *p, long long info[8]) {
   info[5] = tfk::kThreads;
   info[6] = p->launches;
   info[7] = p->hp.inter_rows;
+  return TF_OK;
+}
+
+int tf_plan_set_wait_limit(tf_plan *p, int polls) {
+  if (!p || polls <= 0) return fail(TF_ERR_ARG, "tf_plan_set_wait_limit: bad argument");
+  p->spin_limit = polls;
   return TF_OK;
 }
 

@@ -172,3 +172,27 @@ def bytes_spmm_spmm(n, nnz, ncols):
 
 def bytes_sddmm_spmm(n, nnz, kq, nv):
     return 4 * (2 * n * kq + 2 * n * nv + 2 * nnz + (n + 1))
+
+
+def laplacian_rows(dims, row0: int, row1: int, dtype=np.float32):
+    """Rows [row0, row1) of laplacian(dims) with GLOBAL column ids (what one rank of a row-block
+    partition owns).  Returns (Ap, Ai, Ax) with Ap starting at 0."""
+    dims = tuple(int(d) for d in dims)
+    idx = np.arange(row0, row1, dtype=np.int64)
+    strides, coords, s = [], [], 1
+    for d in dims:
+        strides.append(s)
+        coords.append((idx // s) % d)
+        s *= d
+    cols, valid, vals = [], [], []
+    for k in reversed(range(len(dims))):
+        cols.append(idx - strides[k]); valid.append(coords[k] > 0); vals.append(-1.0)
+    cols.append(idx); valid.append(np.ones(len(idx), dtype=bool)); vals.append(2.0 * len(dims))
+    for k in range(len(dims)):
+        cols.append(idx + strides[k]); valid.append(coords[k] < dims[k] - 1); vals.append(-1.0)
+    valid = np.stack(valid, axis=1)
+    cols = np.stack(cols, axis=1)
+    vals = np.broadcast_to(np.asarray(vals, dtype=dtype), valid.shape)
+    ap = np.zeros(len(idx) + 1, dtype=np.int64)
+    np.cumsum(valid.sum(axis=1), out=ap[1:])
+    return ap.astype(np.int32), cols[valid].astype(np.int64), np.ascontiguousarray(vals[valid])
