@@ -186,6 +186,7 @@ def main():
     ap.add_argument("--slack", type=int, default=-1)
     ap.add_argument("--ring-mb", type=int, default=0)
     ap.add_argument("--ctas-per-sm", type=int, default=0)
+    ap.add_argument("--dims", default="", help="override the per-rank grid, e.g. 128,128,32 (profiling on a small case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -209,7 +210,7 @@ def main():
     wl = WORKLOADS[args.workload]
     chain, n = wl["chain"], wl["n"]
     k = wl.get("k", 0)
-    dims = list(wl["dims"])
+    dims = list(wl["dims"]) if not args.dims else [int(x) for x in args.dims.split(",")]
     strong = args.workload == "c5"
     if not strong and world > 1:
         dims[-1] *= world  # weak scaling: the grid grows along its slowest axis

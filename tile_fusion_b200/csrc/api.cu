@@ -78,7 +78,7 @@ struct tf_plan {
   // host-pointer path staging
   DevBuf<float> h_in0, h_in1, h_in2, h_out;
   int grid = 0, vec = 1, ch = 1;
-  int epoch = 0;
+  int epoch = 1;  // flags start at 0, so no pass may use 0
   int spin_limit = 1 << 22;
   long long launches = 0;
   int device = 0;

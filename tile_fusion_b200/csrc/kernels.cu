@@ -146,6 +146,9 @@ __device__ __forceinline__ void sddmm_row_warp(const Params &P, int row, int lan
 // ---------------------------------------------------------------------------
 // The persistent executor
 // ---------------------------------------------------------------------------
+#ifndef TF_MIN_CTAS
+#define TF_MIN_CTAS 4
+#endif
 constexpr int kHeavyNnz = 64 * kWarps;  // a single-row block at least this heavy is split over the CTA
 
 union StreamSmem {
@@ -154,7 +157,7 @@ union StreamSmem {
 };
 
 template <int MODE, int VEC, int CH, bool RING>
-__global__ void __launch_bounds__(kThreads) stream_kernel(const Params P) {
+__global__ void __launch_bounds__(kThreads, TF_MIN_CTAS) stream_kernel(const Params P) {
   __shared__ StreamSmem sm;
   __shared__ int s_next;
   __shared__ int s_ok;
@@ -174,15 +177,17 @@ __global__ void __launch_bounds__(kThreads) stream_kernel(const Params P) {
     const int kind = ia.x, block = ia.y, rb = ia.z, re = ia.w;
     const int need = ib.x, base = ib.y, send_row = ib.z;
 
-    if (threadIdx.x == 0) {
-      bool ok = true;
-      if (need > 0) ok = wait_for(kind == 1 ? &st->prod_wm : &st->cons_wm, need, st, P.spin_limit);
-      s_ok = ok;
+    if (need > 0) {
+      if (warp == 0) {
+        const bool ok = kind == 1 ? wait_for(&st->prod_wm, P.prod_done, need, P.epoch, st, P.spin_limit, lane)
+                                  : wait_for(&st->cons_wm, P.cons_done, need, P.epoch, st, P.spin_limit, lane);
+        if (lane == 0) s_ok = ok;
+      }
+      __syncthreads();
+      if (!s_ok) break;
+      // order this CTA's reads of T after the acquires made by warp 0
+      asm volatile("fence.acq_rel.gpu;" ::: "memory");
     }
-    __syncthreads();
-    if (!s_ok) break;
-    // order this CTA's reads of T after the acquire made by thread 0
-    asm volatile("fence.acq_rel.gpu;" ::: "memory");
 
     if (kind == 0 || kind == 3) {
       // ---- produce rows [rb, re) of T (kind 3: into the send buffer at row send_row) ----
@@ -201,14 +206,16 @@ __global__ void __launch_bounds__(kThreads) stream_kernel(const Params P) {
         if (re - rb == 1 && __ldg(P.f_ap + re) - __ldg(P.f_ap + rb) >= kHeavyNnz)
           spmm_row_cta<VEC, CH, false, false>(P.f_ap, P.f_ai, P.f_ax, rb, P.in0, P.n_cols, dst_row(rb), false,
                                               0, 0, 0, sm.red);
-        else
-          for (int r = rb + warp; r < re; r += kWarps)
+        else {
+          const int q = (re - rb + kWarps - 1) / kWarps;  // consecutive rows per warp
+          for (int r = rb + warp * q; r < min(re, rb + (warp + 1) * q); ++r)
             spmm_row_warp<VEC, CH, false, false>(P.f_ap, P.f_ai, P.f_ax, r, P.in0, P.n_cols, dst_row(r),
                                                  false, 0, 0, 0, lane);
+        }
       }
       if (kind == 0) {
         __syncthreads();
-        if (threadIdx.x == 0) publish(P.prod_done, &st->prod_wm, block, P.n_prod, P.epoch);
+        if (threadIdx.x == 0) publish(P.prod_done, block, P.epoch);
       }
     } else if (kind == 1) {
       // ---- consume: D[rb, re) = A * T ----
@@ -216,14 +223,16 @@ __global__ void __launch_bounds__(kThreads) stream_kernel(const Params P) {
         spmm_row_cta<VEC, CH, true, RING>(P.s_ap, P.s_ai, P.s_ax, rb, P.inter, P.n_cols,
                                           P.out + (size_t)rb * P.n_cols, P.relu != 0, base, P.ring_rows,
                                           P.m_local, sm.red);
-      else
-        for (int r = rb + warp; r < re; r += kWarps)
+      else {
+        const int q = (re - rb + kWarps - 1) / kWarps;
+        for (int r = rb + warp * q; r < min(re, rb + (warp + 1) * q); ++r)
           spmm_row_warp<VEC, CH, true, RING>(P.s_ap, P.s_ai, P.s_ax, r, P.inter, P.n_cols,
                                              P.out + (size_t)r * P.n_cols, P.relu != 0, base, P.ring_rows,
                                              P.m_local, lane);
+      }
       if (RING) {
         __syncthreads();
-        if (threadIdx.x == 0) publish(P.cons_done, &st->cons_wm, block, P.n_cons, P.epoch);
+        if (threadIdx.x == 0) publish(P.cons_done, block, P.epoch);
       }
     } else {
       // ---- SDDMM-SpMM rows ----
@@ -299,9 +308,10 @@ __global__ void __launch_bounds__(kThreads) spmm_kernel(const int *ap, const int
                                                         const float *x, int n_cols, float *out) {
   const int lane = threadIdx.x & 31;
   const int nw = gridDim.x * kWarps;
-  for (int r = blockIdx.x * kWarps + (threadIdx.x >> 5); r < m; r += nw)
-    spmm_row_warp<VEC, CH, false, false>(ap, ai, ax, r, x, n_cols, out + (size_t)r * n_cols, false, 0, 0, 0,
-                                         lane);
+  // 8 consecutive rows per warp
+  for (int r0 = (blockIdx.x * kWarps + (threadIdx.x >> 5)) * 8; r0 < m; r0 += nw * 8)
+    for (int r = r0; r < min(m, r0 + 8); ++r)
+      spmm_row_warp<VEC, CH, false, false>(ap, ai, ax, r, x, n_cols, out + (size_t)r * n_cols, false, 0, 0, 0, lane);
 }
 
 // ---------------------------------------------------------------------------

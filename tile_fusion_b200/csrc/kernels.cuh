@@ -59,31 +59,39 @@ __device__ __forceinline__ int ld_acquire(const int *p) {
   return v;
 }
 
-// Publish block `b` and move the contiguous watermark as far as the flags allow.
-// The sequentially-consistent fences on both sides of the flag store rule out the
-// store-buffering outcome in which two finishing CTAs each miss the other's flag.
-__device__ __forceinline__ void publish(int *done, int *wm, int b, int nblocks, int epoch) {
+// Publish block `b`: everything the CTA wrote (ordered before by the CTA barrier) is made
+// visible, then the block's flag takes the value of this pass.
+__device__ __forceinline__ void publish(int *done, int b, int epoch) {
   __threadfence();
-  atomicExch(done + b, epoch);
-  __threadfence();
-  int w = ld_acquire(wm);
-  while (w < nblocks && ld_acquire(done + w) == epoch) {
-    const int old = atomicCAS(wm, w, w + 1);
-    w = (old == w) ? w + 1 : old;
-  }
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(done + b), "r"(epoch) : "memory");
 }
 
-// Bounded wait for *wm >= need.  Returns false if it gave up or another CTA already did.
-__device__ __forceinline__ bool wait_for(const int *wm, int need, ExecState *st, int spin_limit) {
+// Bounded wait, executed by one whole warp, until blocks [0, need) of the other side are complete.
+// `wm` is a lazy lower bound of the completed prefix: whoever verifies the flags [wm, need) raises
+// it, so in steady state a waiter reads the watermark and one or two flags.  No thread ever walks
+// the flag array serially.  Returns false if the wait gave up (or another CTA already had).
+__device__ __forceinline__ bool wait_for(int *wm, const int *done, int need, int epoch, ExecState *st,
+                                         int spin_limit, int lane) {
   int spins = 0;
-  while (ld_acquire(wm) < need) {
-    if (++spins > spin_limit || ld_acquire(&st->error) != 0) {
-      atomicExch(&st->error, 1);
+  for (;;) {
+    int w = 0;
+    if (lane == 0) w = ld_acquire(wm);
+    w = __shfl_sync(kFull, w, 0);
+    if (w >= need) return true;
+    bool all = true;
+    for (int b = w + lane; b < need; b += 32) all = all && (ld_acquire(done + b) == epoch);
+    if (__all_sync(kFull, all)) {
+      if (lane == 0) { __threadfence(); atomicMax(wm, need); }
+      return true;
+    }
+    int err = 0;
+    if (lane == 0) err = (++spins > spin_limit) || (ld_acquire(&st->error) != 0);
+    if (__shfl_sync(kFull, err, 0)) {
+      if (lane == 0) atomicExch(&st->error, 1);
       return false;
     }
-    __nanosleep(spins < 64 ? 32 : 256);
+    __nanosleep(spins < 64 ? 64 : 512);
   }
-  return true;
 }
 
 // ---------------------------------------------------------------------------
