@@ -186,6 +186,8 @@ def main():
     ap.add_argument("--slack", type=int, default=-1)
     ap.add_argument("--ring-mb", type=int, default=0)
     ap.add_argument("--ctas-per-sm", type=int, default=0)
+    ap.add_argument("--tile-slots", type=int, default=0)
+    ap.add_argument("--tile-max-bz", type=int, default=0)
     ap.add_argument("--dims", default="", help="override the per-rank grid, e.g. 128,128,32 (profiling on a small case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -224,6 +226,7 @@ def main():
     st = torch.cuda.current_stream().cuda_stream
     mode = api.MODE_STREAM if args.mode == "stream" else api.MODE_UNFUSED
     plan_kw = dict(rows_per_block=args.rows_per_block, slack_blocks=args.slack, ctas_per_sm=args.ctas_per_sm,
+                   tile_slots=args.tile_slots, tile_max_bz=args.tile_max_bz,
                    ring_bytes=args.ring_mb << 20 if args.ring_mb > 0 else (0 if args.ring_mb == 0 else -1))
 
     def fill(t, seed, offset):
@@ -362,7 +365,7 @@ def main():
                 "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": wl["label"], "grid": "x".join(map(str, dims)), "rows": n_rows,
                            "rows_per_gpu": m, "mode": args.mode, "ring_rows": info["ring_rows"], "grid_ctas": info["grid"],
-                           "items": info["items"], "l2": "inputs (>= 1 GB per step) exceed the 126 MB L2; no flush",
+                           "items": info["items"], "tiles": plan.tile_info(), "l2": "inputs (>= 1 GB per step) exceed the 126 MB L2; no flush",
                            "partition": f"row blocks over {world} GPU(s), halo rows of the intermediate over NCCL"},
                 "clocks": clk.summary(), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
                 "gpu_launches": int(launches_per_step * args.steps)}

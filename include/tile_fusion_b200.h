@@ -119,6 +119,9 @@ typedef struct {
                              appended after the m local rows (multi-GPU); 0 otherwise   */
   int n_boundary;         /* number of entries of `boundary_rows`                       */
   const int *boundary_rows; /* local intermediate rows other ranks need first (sorted)  */
+  int tile_slots;         /* gather tiles: dense-row segments (128 B) a tile may stage in shared
+                             memory; 0 = default, <0 = never tile (gather from global memory)      */
+  int tile_max_bz;        /* gather tiles: most grid planes a tile may span, 0 = default           */
 } tf_plan_opts;
 
 typedef struct tf_plan tf_plan;
@@ -145,6 +148,15 @@ int tf_plan_preview(const tf_csr *A, const tf_csr *B, int producer_is_gemm, int 
                     const tf_plan_opts *o, int resident_ctas, int **items_out, long long *n_items,
                     long long info[8]);
 void tf_free(void *p);
+/* Host-only: the gather tiles the library would build for operator A.  Arrays are malloc'd
+ * (tf_free): row_ptr[n_tiles+1] into rows[], halo_ptr[n_tiles+1] into halo[] (staged source rows in
+ * slot order).  n_tiles = 0 when tiling is declined.  info = {bx, by, bz, 1000 * nonzeros per staged
+ * row}.  No counterpart in the reference. */
+int tf_tiling_preview(const tf_csr *A, int tile_slots, int tile_max_bz, int **row_ptr, int **rows,
+                      int **halo_ptr, int **halo, int *n_tiles, int info[4]);
+/* info = {bx, by, bz, tiles} of the first operator's gather tiles, then the same for the second
+ * operator's (zeros where an operator is not tiled). */
+int tf_plan_tile_info(const tf_plan *p, int info[8]);
 
 /* info[0] items, [1] producer blocks, [2] consumer blocks, [3] ring rows (0 = full-size
  * intermediate), [4] grid CTAs, [5] threads per CTA, [6] kernels launched by the last call,

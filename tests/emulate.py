@@ -20,8 +20,10 @@ def _spmm_rows(ap, ai, ax, rows, dense_row):
     return out
 
 
-def run_items(items, info, first, second, C, n_cols, m_local, window=16, seed=0, produce=None):
+def run_items(items, info, first, second, C, n_cols, m_local, window=16, seed=0, produce=None, ptile=None,
+              ctile=None):
     """first/second: (ap, ai, ax).  produce(r) overrides the producer row (dense producer).
+    ptile / ctile: (row_ptr, rows, halo_ptr, halo) of the gather tiles when items of kind 4 / 5 occur.
     Returns D (float64) and the intermediate tag array used for the checks."""
     rng = np.random.default_rng(seed)
     ring = info["ring_rows"]
@@ -42,19 +44,24 @@ def run_items(items, info, first, second, C, n_cols, m_local, window=16, seed=0,
         ready = []
         for t in active:
             kind, block, rb, re, need, base = items[t][:6]
-            wm = pw if kind == 1 else cw
+            wm = pw if kind in (1, 5) else cw
             if need <= wm:
                 ready.append(t)
         assert ready, "deadlock: no in-flight item is ready"
         t = ready[rng.integers(len(ready))]
         active.remove(t)
         kind, block, rb, re, need, base = items[t][:6]
-        if kind == 0:
-            pbase = (rb // ring) * ring if ring else 0
-            for r in range(rb, re):
+        if kind in (0, 4):
+            rows = range(rb, re) if kind == 0 else ptile[1][ptile[0][rb]:ptile[0][rb + 1]]
+            if kind == 4:  # a tiled producer may only touch the source rows it staged
+                staged = set(ptile[3][ptile[2][rb]:ptile[2][rb + 1]].tolist())
+                for r in rows:
+                    assert set(first[1][first[0][r]:first[0][r + 1]].tolist()) <= staged
+            for r in rows:
                 slot = r
                 if ring:
-                    slot = r - pbase
+                    slot = r - base
+                    assert 0 <= slot < 2 * ring, "producer row outside the item's ring window"
                     if slot >= ring:
                         slot -= ring
                 if produce is not None:
@@ -68,8 +75,13 @@ def run_items(items, info, first, second, C, n_cols, m_local, window=16, seed=0,
             pdone[block] = True
             while pw < n_prod and pdone[pw]:
                 pw += 1
-        elif kind == 1:
-            for r in range(rb, re):
+        elif kind in (1, 5):
+            rows = range(rb, re) if kind == 1 else ctile[1][ctile[0][rb]:ctile[0][rb + 1]]
+            if kind == 5:
+                staged = set(ctile[3][ctile[2][rb]:ctile[2][rb + 1]].tolist())
+                for r in rows:
+                    assert set(second[1][second[0][r]:second[0][r + 1]].tolist()) <= staged
+            for r in rows:
                 acc = np.zeros(n_cols)
                 for p in range(second[0][r], second[0][r + 1]):
                     col = second[1][p]

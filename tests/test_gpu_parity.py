@@ -65,10 +65,14 @@ def test_spmm_spmm_all_modes(torch_cuda, oracle, mat, n_cols):
     want, _ = oracle.spmm_spmm(a, a, c, oracle.inspect_fixed(a[0], a[1], 2, 64))
     cd = _dev(torch, c)
     results = {}
-    variants = [("stream_ring", dict(mode=api.MODE_STREAM, rows_per_block=16, slack_blocks=4, ring_bytes=1 << 30)),
+    variants = [("stream_ring", dict(mode=api.MODE_STREAM, rows_per_block=16, slack_blocks=4, ring_bytes=1 << 30,
+                                     tile_slots=-1)),
                 ("stream_default", dict(mode=api.MODE_STREAM)),
-                ("stream_noring", dict(mode=api.MODE_STREAM, ring_bytes=-1, rows_per_block=8)),
-                ("unfused", dict(mode=api.MODE_UNFUSED)),
+                ("stream_noring", dict(mode=api.MODE_STREAM, ring_bytes=-1, rows_per_block=8, tile_slots=-1)),
+                ("tiled_ring", dict(mode=api.MODE_STREAM, tile_slots=160, tile_max_bz=2, ring_bytes=1 << 30,
+                                    slack_blocks=3)),
+                ("tiled_unfused", dict(mode=api.MODE_UNFUSED, tile_slots=400)),
+                ("unfused", dict(mode=api.MODE_UNFUSED, tile_slots=-1)),
                 ("sched_fixed", dict(mode=api.MODE_SCHEDULE, schedule=_sched(A, 1, n_cols))),
                 ("sched_vt", dict(mode=api.MODE_SCHEDULE, schedule=_sched(A, 2, n_cols)))]
     for name, kw in variants:
@@ -81,6 +85,10 @@ def test_spmm_spmm_all_modes(torch_cuda, oracle, mat, n_cols):
         common.assert_close(results[name], want, f"{mat} N={n_cols} {name}")
         if name == "stream_ring" and mat.startswith("lap"):
             assert 0 < plan.info()["ring_rows"] < A.M
+        if name == "tiled_unfused" and mat.startswith("lap") and n_cols % 4 == 0:
+            assert plan.tile_info()["consumer"][3] > 0, plan.tile_info()
+        if name == "tiled_ring" and mat.startswith("lap"):
+            assert 0 < plan.info()["ring_rows"] < A.M, plan.info()
         plan.close()
     # every mode adds the same products in the same order (rows heavy enough to be split over a
     # CTA in stream mode are reduced in another order, so the graph case is left out)

@@ -30,7 +30,7 @@ def test_stream_plan_emulation(built_lib, dims, rb, slack, ring_bytes, window):
     n, nc = A.M, 3
     C = synth.uniform(7, (n, nc)).astype(np.float64)
     items, info = api.plan_preview(A, n_cols=nc, rows_per_block=rb, slack_blocks=slack, ring_bytes=ring_bytes,
-                                   resident_ctas=window)
+                                   resident_ctas=window, tile_slots=-1)
     if ring_bytes > 0:
         assert 0 < info["ring_rows"] < n, info
     else:
@@ -60,7 +60,7 @@ def test_heavy_rows_get_their_own_block(built_lib):
     ai = np.concatenate(rows)
     ax = np.ones(len(ai), np.float32)
     A = api.CSRMatrix(n, n, ap, ai, ax)
-    items, info = api.plan_preview(A, n_cols=4, rows_per_block=8, slack_blocks=1)
+    items, info = api.plan_preview(A, n_cols=4, rows_per_block=8, slack_blocks=1, tile_slots=-1)
     cons = items[items[:, 0] == 1]
     blk = cons[(cons[:, 2] <= 17) & (cons[:, 3] > 17)][0]
     assert blk[3] - blk[2] == 1  # 300 nnz > 8*32: the heavy row stands alone
@@ -70,7 +70,7 @@ def test_heavy_rows_get_their_own_block(built_lib):
 def test_unfused_mode_lists_all_producers_first(built_lib):
     t = synth.laplacian((12, 12))
     A = _csr(t)
-    items, info = api.plan_preview(A, n_cols=8, rows_per_block=8, mode=api.MODE_UNFUSED)
+    items, info = api.plan_preview(A, n_cols=8, rows_per_block=8, mode=api.MODE_UNFUSED, tile_slots=-1)
     k = info["producer_blocks"]
     assert (items[:k, 0] == 0).all() and (items[k:, 0] == 1).all() and info["ring_rows"] == 0
 
@@ -95,9 +95,45 @@ def test_halo_plan_defers_halo_consumers(built_lib):
                       np.array(vals, np.float32))
     boundary = np.array(list(range(0, plane)) + list(range(m - plane, m)), np.int32)
     items, info = api.plan_preview(A, producer_is_gemm=True, n_cols=4, rows_per_block=16, slack_blocks=1,
-                                   halo_rows=len(halo_ids), boundary_rows=boundary)
+                                   halo_rows=len(halo_ids), boundary_rows=boundary, tile_slots=-1)
     assert info["ring_rows"] == 0 and info["intermediate_rows"] == m + len(halo_ids)
     p1 = items[info["phase1_begin"]:info["phase2_begin"]]
     p2 = items[info["phase2_begin"]:info["end"]]
     assert (p2[:, 0] == 1).all() and len(p2) == 2 * plane // 16  # first and last plane read halo rows
     assert (p1[:, 0] == 0).sum() == m // 16 and (p1[:, 0] == 1).sum() == 0  # 2 planes: every consumer touches a halo
+
+
+@pytest.mark.parametrize("dims,slots,max_bz,ring_bytes,slack,window", [
+    ((24, 20, 12), 200, 2, 1 << 30, 3, 10),   # 3-D bricks through a ring
+    ((24, 20, 12), 300, 4, -1, 3, 10),        # 3-D bricks, full intermediate
+    ((40, 36), 120, 1, 1 << 30, 2, 8),        # 2-D bricks through a ring
+    ((500,), 80, 1, 1 << 30, 2, 6),           # 1-D
+])
+def test_tiled_plan_emulation(built_lib, dims, slots, max_bz, ring_bytes, slack, window):
+    """Gather tiles: every tile stages all the source rows its rows name, every row is in exactly one
+    tile, and the ticket order / ring waits hold under random interleavings."""
+    t = synth.laplacian(dims)
+    A = _csr(t)
+    n, nc = A.M, 4
+    til = api.tiling_preview(A, tile_slots=slots, tile_max_bz=max_bz)
+    assert til is not None
+    row_ptr, rows, halo_ptr, halo, tinfo = til
+    assert sorted(rows.tolist()) == list(range(n))
+    assert (np.diff(halo_ptr) <= slots).all() and tinfo["reuse"] >= 2.0
+    items, info = api.plan_preview(A, n_cols=nc, slack_blocks=slack, ring_bytes=ring_bytes, resident_ctas=window,
+                                   tile_slots=slots, tile_max_bz=max_bz)
+    assert set(items[:, 0].tolist()) == {4, 5}
+    if ring_bytes > 0:
+        assert 0 < info["ring_rows"] < n, info
+    C = synth.uniform(7, (n, nc)).astype(np.float64)
+    want = _dense_chain(t, C)
+    for seed in range(2):
+        D, _ = run_items(items, info, t, t, C, nc, n, window=window, seed=seed, ptile=til[:4], ctile=til[:4])
+        np.testing.assert_allclose(D, want, rtol=1e-12, atol=1e-12)
+
+
+def test_tiling_declined_without_structure(built_lib):
+    g = synth.rmat_gcn(3, 3000, 10)
+    assert api.tiling_preview(api.CSRMatrix(3000, 3000, *g)) is None
+    items, info = api.plan_preview(api.CSRMatrix(3000, 3000, *g), n_cols=32)
+    assert set(items[:, 0].tolist()) == {0, 1}

@@ -32,7 +32,8 @@ class Csr(C.Structure):
 class PlanOpts(C.Structure):
     _fields_ = [("mode", C.c_int), ("rows_per_block", C.c_int), ("ring_bytes", C.c_int),
                 ("slack_blocks", C.c_int), ("ctas_per_sm", C.c_int), ("halo_rows", C.c_int),
-                ("n_boundary", C.c_int), ("boundary_rows", C.c_void_p)]
+                ("n_boundary", C.c_int), ("boundary_rows", C.c_void_p), ("tile_slots", C.c_int),
+                ("tile_max_bz", C.c_int)]
 
 
 EXPORTS = [
@@ -41,7 +42,7 @@ EXPORTS = [
     "tf_schedule_free", "tf_plan_spmm_spmm", "tf_plan_gemm_spmm", "tf_plan_sddmm_spmm", "tf_plan_free",
     "tf_plan_info", "tf_plan_status", "tf_exec_spmm_spmm", "tf_exec_gemm_spmm", "tf_exec_sddmm_spmm",
     "tf_exec_phase", "tf_plan_intermediate", "tf_plan_exchange_buffers", "tf_spmm_spmm_host", "tf_gemm_spmm_host",
-    "tf_sddmm_spmm_host", "tf_spmm_dev", "tf_fill_uniform", "tf_fill_normal", "tf_plan_preview", "tf_free", "tf_plan_set_wait_limit",
+    "tf_sddmm_spmm_host", "tf_spmm_dev", "tf_fill_uniform", "tf_fill_normal", "tf_plan_preview", "tf_free", "tf_plan_set_wait_limit", "tf_tiling_preview", "tf_plan_tile_info",
 ]
 
 _lib = None
@@ -93,6 +94,8 @@ def lib() -> C.CDLL:
                                   C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]
     L.tf_free.argtypes = [vp]
     L.tf_plan_set_wait_limit.argtypes = [vp, i]
+    L.tf_tiling_preview.argtypes = [C.POINTER(Csr), i, i] + [C.POINTER(vp)] * 4 + [ip, ip]
+    L.tf_plan_tile_info.argtypes = [vp, ip]
     L.tf_free.restype = None
     _lib = L
     return L

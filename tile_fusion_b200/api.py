@@ -186,13 +186,14 @@ class Plan:
     def __init__(self, chain: str, A: CSRMatrix, *, B: CSRMatrix | None = None, k: int = 0, n_cols: int = 0,
                  mode: int = MODE_STREAM, schedule: FusedSchedule | None = None, rows_per_block: int = 0,
                  ring_bytes: int = 0, slack_blocks: int = -1, ctas_per_sm: int = 0, halo_rows: int = 0,
-                 boundary_rows=None):
+                 boundary_rows=None, tile_slots: int = 0, tile_max_bz: int = 0):
         L = _lib.lib()
         self.chain, self.A, self.B = chain, A, B
         self.n_cols, self.k = int(n_cols), int(k)
         br = _i32(boundary_rows) if boundary_rows is not None and len(boundary_rows) else None
         o = _lib.PlanOpts(mode, rows_per_block, ring_bytes, slack_blocks, ctas_per_sm, halo_rows,
-                          0 if br is None else br.shape[0], None if br is None else br.ctypes.data)
+                          0 if br is None else br.shape[0], None if br is None else br.ctypes.data,
+                          tile_slots, tile_max_bz)
         h = C.c_void_p()
         ca = A._c()
         sh = schedule._h if schedule is not None else None
@@ -220,6 +221,12 @@ class Plan:
     def status(self, stream: int | None = None) -> None:
         """Waits for the plan's work and raises if a bounded in-kernel wait ran out."""
         check(_lib.lib().tf_plan_status(self._h, stream if stream is not None else _stream_ptr()))
+
+    def tile_info(self) -> dict:
+        """Brick shape and tile count of the gather tiles of the first and second operator."""
+        a = (C.c_int * 8)()
+        check(_lib.lib().tf_plan_tile_info(self._h, a))
+        return {"producer": tuple(a[0:4]), "consumer": tuple(a[4:8])}
 
     def set_wait_limit(self, polls: int) -> None:
         check(_lib.lib().tf_plan_set_wait_limit(self._h, int(polls)))
@@ -362,12 +369,12 @@ def gcn_forward(A: CSRMatrix, X, W1, W2, plans=None):
 
 def plan_preview(A: CSRMatrix, B: CSRMatrix | None = None, *, producer_is_gemm=False, n_cols=128,
                  resident_ctas=592, mode=MODE_STREAM, rows_per_block=0, ring_bytes=0, slack_blocks=-1,
-                 halo_rows=0, boundary_rows=None):
+                 halo_rows=0, boundary_rows=None, tile_slots=0, tile_max_bz=0):
     """Host-only: the item list the stream executor would walk, as an (n, 8) int array
     {kind, block, row_begin, row_end, need, base, aux0, aux1}, plus an info dict."""
     br = _i32(boundary_rows) if boundary_rows is not None and len(boundary_rows) else None
     o = _lib.PlanOpts(mode, rows_per_block, ring_bytes, slack_blocks, 0, halo_rows,
-                      0 if br is None else br.shape[0], None if br is None else br.ctypes.data)
+                      0 if br is None else br.shape[0], None if br is None else br.ctypes.data, tile_slots, tile_max_bz)
     ca = A._c()
     cb = B._c() if B is not None else None
     items, n = C.c_void_p(), C.c_longlong()
@@ -379,3 +386,26 @@ def plan_preview(A: CSRMatrix, B: CSRMatrix | None = None, *, producer_is_gemm=F
     keys = ["items", "producer_blocks", "consumer_blocks", "ring_rows", "phase1_begin", "phase2_begin", "end",
             "intermediate_rows"]
     return arr[:n.value * 8].reshape(-1, 8), dict(zip(keys, [int(x) for x in info]))
+
+
+def tiling_preview(A: CSRMatrix, tile_slots=0, tile_max_bz=0):
+    """Host-only: the gather tiles of operator A as (row_ptr, rows, halo_ptr, halo, info) or None."""
+    ca = A._c()
+    ptrs = [C.c_void_p() for _ in range(4)]
+    n, info = C.c_int(), (C.c_int * 4)()
+    check(_lib.lib().tf_tiling_preview(C.byref(ca), tile_slots, tile_max_bz, *[C.byref(p) for p in ptrs], C.byref(n), info))
+
+    def take(p, count):
+        arr = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_int)), shape=(max(count, 1),)).copy()[:count]
+        _lib.lib().tf_free(p)
+        return arr
+    if n.value == 0:
+        for p in ptrs:
+            _lib.lib().tf_free(p)
+        return None
+    row_ptr = take(ptrs[0], n.value + 1)
+    halo_ptr_raw = ptrs[2]
+    rows = take(ptrs[1], int(row_ptr[-1]))
+    halo_ptr = take(halo_ptr_raw, n.value + 1)
+    halo = take(ptrs[3], int(halo_ptr[-1]))
+    return row_ptr, rows, halo_ptr, halo, dict(bx=info[0], by=info[1], bz=info[2], reuse=info[3] / 1000.0)

@@ -70,6 +70,30 @@ struct tf_plan {
   DevBuf<int> prod_done, cons_done;
   DevBuf<tfk::ExecState> state;
   DevBuf<float> inter, sendbuf;
+  // gather tiles (stream / unfused mode)
+  struct DevTiling {
+    DevBuf<int> row_ptr, rows, halo_ptr, halo;
+    DevBuf<unsigned short> slot;
+    bool on = false;
+    int upload(const tf::Tiling &t) {
+      on = t.tiled;
+      if (!on) return TF_OK;
+      int rc = row_ptr.upload(t.tile_row_ptr);
+      if (rc == TF_OK) rc = rows.upload(t.rows);
+      if (rc == TF_OK) rc = halo_ptr.upload(t.tile_halo_ptr);
+      if (rc == TF_OK) rc = halo.upload(t.halo);
+      if (rc == TF_OK) rc = slot.upload(t.slot);
+      return rc;
+    }
+    tfk::TileArrays view() const {
+      tfk::TileArrays a{nullptr, nullptr, nullptr, nullptr, nullptr};
+      if (on) a = tfk::TileArrays{row_ptr.p, rows.p, halo_ptr.p, halo.p, slot.p};
+      return a;
+    }
+  } ptile, ctile;
+  size_t dyn_smem = 0;
+  int tile_slots = 0;
+  int tile_info[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // producer bx,by,bz,tiles ; consumer bx,by,bz,tiles
   // schedule mode
   DevBuf<int> s_ptr2, s_id, s_type, s_ker;
   int s_n1 = 0;
@@ -115,7 +139,8 @@ int upload_items(tf_plan &p) {
 int finish_plan(tf_plan &p, const tf_plan_opts &o, int sm_count, bool ring) {
   const bool a16 = true;  // buffers owned by the plan are 256-byte aligned; callers' pointers are checked per call
   tfk::choose_shape(p.n_cols, a16, &p.vec, &p.ch);
-  int occ = tfk::stream_occupancy(p.chain, p.vec, p.ch, ring);
+  if (p.dyn_smem > 0) { p.vec = 4; p.ch = 1; }
+  int occ = tfk::stream_occupancy(p.chain, p.vec, p.ch, ring, p.dyn_smem);
   if (occ <= 0) return fail(TF_ERR_CUDA, "occupancy query failed for the executor kernel");
   if (o.ctas_per_sm > 0) occ = std::min(occ, o.ctas_per_sm);
   p.grid = sm_count * occ;
@@ -126,8 +151,7 @@ int zero_state(tf_plan &p) {
   int rc = p.state.alloc(1);
   if (rc != TF_OK) return rc;
   TF_CUDA(cudaMemset(p.state.p, 0, sizeof(tfk::ExecState)));
-  const size_t np = p.hp.prod_rows.empty() ? 0 : p.hp.prod_rows.size() - 1;
-  const size_t nc = p.hp.cons_rows.empty() ? 0 : p.hp.cons_rows.size() - 1;
+  const size_t np = (size_t)p.hp.n_prod, nc = (size_t)p.hp.n_cons;
   rc = p.prod_done.alloc(std::max<size_t>(np, 1));
   if (rc == TF_OK) rc = p.cons_done.alloc(std::max<size_t>(nc, 1));
   if (rc != TF_OK) return rc;
@@ -142,6 +166,7 @@ int check_opts(const tf_plan_opts *o, tf_plan_opts &out) {
   if (o) out = *o;
   if (out.mode < TF_MODE_STREAM || out.mode > TF_MODE_UNFUSED) return fail(TF_ERR_ARG, "plan: unknown mode");
   if (out.rows_per_block < 0 || out.halo_rows < 0 || out.n_boundary < 0) return fail(TF_ERR_ARG, "plan: negative option");
+  if (out.tile_slots > tfk::kTileMaxSlots) return fail(TF_ERR_ARG, "plan: tile_slots above the shared-memory capacity");
   if (out.n_boundary > 0 && !out.boundary_rows) return fail(TF_ERR_ARG, "plan: boundary_rows is null");
   return TF_OK;
 }
@@ -233,7 +258,27 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
   if (rc != TF_OK) return rc;
   pp.max_ctas = p->grid;
   pp.slack_blocks = o.mode == TF_MODE_UNFUSED ? (1 << 30) : o.slack_blocks;
-  rc = tf::build_stream_plan(pp, F ? F->ap : nullptr, F ? F->ai : nullptr, A->ap, A->ai, p->hp);
+  // gather tiles: 16-byte staging copies need rows that are multiples of 4 floats
+  tf::Tiling pt, ct;
+  const int slots = o.tile_slots == 0 ? tf::kDefaultTileSlots : o.tile_slots;
+  if (o.mode != TF_MODE_SCHEDULE && slots > 0 && n_cols % 4 == 0) {
+    const int max_bz = o.tile_max_bz > 0 ? o.tile_max_bz : tf::kDefaultTileMaxBz;
+    if (F) tf::build_tiling(F->m, F->ap, F->ai, slots, max_bz, pt);
+    tf::build_tiling(A->m, A->ap, A->ai, slots, max_bz, ct);
+    if (pt.tiled || ct.tiled) {
+      p->dyn_smem = (size_t)slots * 132;  // 128 B of staging + one source row id per slot
+      p->tile_slots = slots;
+      rc = finish_plan(*p, o, sm_count, false);  // the staging buffer lowers the resident CTA count
+      if (rc != TF_OK) return rc;
+      pp.max_ctas = p->grid;
+    }
+  }
+  p->tile_info[0] = pt.bx; p->tile_info[1] = pt.by; p->tile_info[2] = pt.bz; p->tile_info[3] = pt.tiles();
+  p->tile_info[4] = ct.bx; p->tile_info[5] = ct.by; p->tile_info[6] = ct.bz; p->tile_info[7] = ct.tiles();
+  rc = tf::build_stream_plan(pp, F ? F->ap : nullptr, F ? F->ai : nullptr, A->ap, A->ai, &pt, &ct, p->hp);
+  if (rc != TF_OK) return rc;
+  rc = p->ptile.upload(pt);
+  if (rc == TF_OK) rc = p->ctile.upload(ct);
   if (rc != TF_OK) return rc;
   rc = finish_plan(*p, o, sm_count, p->hp.ring_rows > 0);
   if (rc != TF_OK) return rc;
@@ -284,8 +329,11 @@ tfk::Params base_params(tf_plan &p) {
   P.st = p.state.p;
   P.n_cols = p.n_cols; P.k_dim = p.k_dim; P.m_local = p.m;
   P.ring_rows = (int)p.hp.ring_rows;
-  P.n_prod = p.hp.prod_rows.empty() ? 0 : (int)p.hp.prod_rows.size() - 1;
-  P.n_cons = p.hp.cons_rows.empty() ? 0 : (int)p.hp.cons_rows.size() - 1;
+  P.n_prod = p.hp.n_prod;
+  P.n_cons = p.hp.n_cons;
+  P.pt = p.ptile.view();
+  P.ct = p.ctile.view();
+  P.tile_slots = p.tile_slots;
   P.spin_limit = p.spin_limit;
   return P;
 }
@@ -299,9 +347,18 @@ void call_shape(const tf_plan &p, std::initializer_list<const void *> ptrs, int 
   tfk::choose_shape(p.n_cols, a16, vec, ch);
 }
 
+int check_tiled_alignment(const tf_plan &p, const tfk::Params &P) {
+  if ((p.ptile.on || p.ctile.on) && !(aligned(P.in0, 16) && (!P.out || aligned(P.out, 16))))
+    return fail(TF_ERR_ARG, "gather tiles need 16-byte aligned dense operands (build the plan with tile_slots < 0 otherwise)");
+  return TF_OK;
+}
+
 int run_phases(tf_plan &p, tfk::Params &P, int first_phase, int last_phase, cudaStream_t s) {
   int vec, ch;
   call_shape(p, {P.in0, P.in1, P.in2, P.out}, &vec, &ch);
+  int rca = check_tiled_alignment(p, P);
+  if (rca != TF_OK) return rca;
+  if (p.dyn_smem > 0) { vec = 4; ch = 1; }  // the tiled kernel variant; its direct items loop over panels
   const bool ring = p.hp.ring_rows > 0;
   if (first_phase <= 1 && last_phase >= 1) ++p.epoch;  // a new pass over the producer blocks
   P.epoch = p.epoch;
@@ -313,7 +370,7 @@ int run_phases(tf_plan &p, tfk::Params &P, int first_phase, int last_phase, cuda
     tfk::Params Q = P;
     if (ph == 0) Q.inter = p.sendbuf.p;
     Q.reset_wm = (ph == 2) || (ph == 1 && p.hp.phase_begin[3] == p.hp.phase_begin[2] && last_phase >= 1);
-    TF_CUDA(tfk::launch_stream(p.chain, vec, ch, ring, p.grid, Q, s));
+    TF_CUDA(tfk::launch_stream(p.chain, vec, ch, ring, p.grid, p.dyn_smem, Q, s));
     ++p.launches;
   }
   return TF_OK;
@@ -323,15 +380,18 @@ int run_unfused(tf_plan &p, tfk::Params &P, cudaStream_t s) {
   // all producers are listed before all consumers: one launch per half, T through HBM
   int vec, ch;
   call_shape(p, {P.in0, P.in1, P.in2, P.out}, &vec, &ch);
+  int rca = check_tiled_alignment(p, P);
+  if (rca != TF_OK) return rca;
+  if (p.dyn_smem > 0) { vec = 4; ch = 1; }
   ++p.epoch;
   P.epoch = p.epoch;
   const int np = P.n_prod;
   p.launches = 0;
   tfk::Params Q = P;
   Q.item_begin = 0; Q.item_end = np; Q.reset_wm = 0;
-  TF_CUDA(tfk::launch_stream(p.chain, vec, ch, false, p.grid, Q, s));
+  TF_CUDA(tfk::launch_stream(p.chain, vec, ch, false, p.grid, p.dyn_smem, Q, s));
   Q.item_begin = np; Q.item_end = (int)p.hp.items.size(); Q.reset_wm = 1;
-  TF_CUDA(tfk::launch_stream(p.chain, vec, ch, false, p.grid, Q, s));
+  TF_CUDA(tfk::launch_stream(p.chain, vec, ch, false, p.grid, p.dyn_smem, Q, s));
   p.launches = 2;
   return TF_OK;
 }
@@ -415,13 +475,19 @@ void tf_plan_free(tf_plan *p) { delete p; }
 int tf_plan_info(const tf_plan *p, long long info[8]) {
   if (!p || !info) return fail(TF_ERR_ARG, "tf_plan_info: null argument");
   info[0] = (long long)p->hp.items.size();
-  info[1] = p->hp.prod_rows.empty() ? 0 : (long long)p->hp.prod_rows.size() - 1;
-  info[2] = p->hp.cons_rows.empty() ? 0 : (long long)p->hp.cons_rows.size() - 1;
+  info[1] = p->hp.n_prod;
+  info[2] = p->hp.n_cons;
   info[3] = p->hp.ring_rows;
   info[4] = p->grid;
-  info[5] = tfk::kThreads;
+  info[5] = p->dyn_smem > 0 ? tfk::kTiledThreads : tfk::kThreads;
   info[6] = p->launches;
   info[7] = p->hp.inter_rows;
+  return TF_OK;
+}
+
+int tf_plan_tile_info(const tf_plan *p, int info[8]) {
+  if (!p || !info) return fail(TF_ERR_ARG, "tf_plan_tile_info: null argument");
+  for (int i = 0; i < 8; ++i) info[i] = p->tile_info[i];
   return TF_OK;
 }
 

@@ -23,7 +23,9 @@ template <class DstRow>
 __device__ __forceinline__ void gemm_rows_cta(const float *__restrict__ B, const float *__restrict__ W,
                                               bool w_t, int rb, int re, int K, int N, DstRow dst_row,
                                               GemmSmem &sm) {
-  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  // written for 256 threads; in a larger CTA the others only take part in the barriers
+  const int tid = threadIdx.x, tx = tid & 15, ty = (tid >> 4) & 15;
+  const bool on = tid < 256;
   for (int r0 = rb; r0 < re; r0 += GM) {
     for (int c0 = 0; c0 < N; c0 += GN) {
       float acc[4][4];
@@ -33,7 +35,7 @@ __device__ __forceinline__ void gemm_rows_cta(const float *__restrict__ B, const
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
       for (int k0 = 0; k0 < K; k0 += GK) {
         // A slice: 64 rows x 16 k; thread loads 4 consecutive k of one row
-        {
+        if (on) {
           const int r = tid >> 2, kk = (tid & 3) * 4;
           const int row = r0 + r;
 #pragma unroll
@@ -43,7 +45,7 @@ __device__ __forceinline__ void gemm_rows_cta(const float *__restrict__ B, const
           }
         }
         // B slice: 16 k x 64 cols; thread loads 4 consecutive cols of one k
-        {
+        if (on) {
           const int kk = tid >> 4, cc = (tid & 15) * 4;
           const int k = k0 + kk;
 #pragma unroll
@@ -72,7 +74,7 @@ __device__ __forceinline__ void gemm_rows_cta(const float *__restrict__ B, const
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int row = r0 + ty * 4 + i;
-        if (row < re) {
+        if (on && row < re) {
           float *d = dst_row(row);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -153,14 +155,21 @@ constexpr int kHeavyNnz = 64 * kWarps;  // a single-row block at least this heav
 
 union StreamSmem {
   GemmSmem g;
-  float red[kWarps * 32 * 8];  // VEC*CH <= 8
+  float red[2048];  // warps * 32 * VEC * CH: 8 * 256 (direct) or 16 * 128 (gather-tile variant)
 };
 
-template <int MODE, int VEC, int CH, bool RING>
-__global__ void __launch_bounds__(kThreads, TF_MIN_CTAS) stream_kernel(const Params P) {
+// TILED: the plan holds gather tiles (item kinds 4 and 5); their staging buffer allows two CTAs per
+// SM, so that variant may use twice the registers.
+template <int MODE, int VEC, int CH, bool RING, bool TILED>
+__global__ void __launch_bounds__(TILED ? kTiledThreads : kThreads, TILED ? 2 : TF_MIN_CTAS)
+    stream_kernel(const Params P) {
+  constexpr int NT = TILED ? kTiledThreads : kThreads;
+  constexpr int NW = NT / 32;
   __shared__ StreamSmem sm;
   __shared__ int s_next;
   __shared__ int s_ok;
+  extern __shared__ float4 stage[];  // gather tiles: tile_slots * 8 float4, then tile_slots source row ids
+  int *hrow = reinterpret_cast<int *>(stage + (size_t)P.tile_slots * 8);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   ExecState *st = P.st;
   const int n_items = P.item_end - P.item_begin;
@@ -179,8 +188,9 @@ __global__ void __launch_bounds__(kThreads, TF_MIN_CTAS) stream_kernel(const Par
 
     if (need > 0) {
       if (warp == 0) {
-        const bool ok = kind == 1 ? wait_for(&st->prod_wm, P.prod_done, need, P.epoch, st, P.spin_limit, lane)
-                                  : wait_for(&st->cons_wm, P.cons_done, need, P.epoch, st, P.spin_limit, lane);
+        const bool ok = (kind == 1 || kind == 5)
+                            ? wait_for(&st->prod_wm, P.prod_done, need, P.epoch, st, P.spin_limit, lane)
+                            : wait_for(&st->cons_wm, P.cons_done, need, P.epoch, st, P.spin_limit, lane);
         if (lane == 0) s_ok = ok;
       }
       __syncthreads();
@@ -194,7 +204,7 @@ __global__ void __launch_bounds__(kThreads, TF_MIN_CTAS) stream_kernel(const Par
       float *dst_base;
       int ring = 0, pbase = 0;
       if (kind == 3) dst_base = P.inter + (ptrdiff_t)(send_row - rb) * P.n_cols;  // phase 0: `inter` is the send buffer
-      else { dst_base = P.inter; if (RING) { ring = P.ring_rows; pbase = (rb / ring) * ring; } }
+      else { dst_base = P.inter; if (RING) { ring = P.ring_rows; pbase = base; } }
       auto dst_row = [&](int r) -> float * {
         int t = r;
         if (RING && kind == 0) { t = r - pbase; if (t >= ring) t -= ring; }
@@ -204,10 +214,10 @@ __global__ void __launch_bounds__(kThreads, TF_MIN_CTAS) stream_kernel(const Par
         gemm_rows_cta(P.in0, P.in1, P.w_transposed != 0, rb, re, P.k_dim, P.n_cols, dst_row, sm.g);
       } else {
         if (re - rb == 1 && __ldg(P.f_ap + re) - __ldg(P.f_ap + rb) >= kHeavyNnz)
-          spmm_row_cta<VEC, CH, false, false>(P.f_ap, P.f_ai, P.f_ax, rb, P.in0, P.n_cols, dst_row(rb), false,
+          spmm_row_cta<NT, VEC, CH, false, false>(P.f_ap, P.f_ai, P.f_ax, rb, P.in0, P.n_cols, dst_row(rb), false,
                                               0, 0, 0, sm.red);
         else {
-          const int q = (re - rb + kWarps - 1) / kWarps;  // consecutive rows per warp
+          const int q = (re - rb + NW - 1) / NW;  // consecutive rows per warp
           for (int r = rb + warp * q; r < min(re, rb + (warp + 1) * q); ++r)
             spmm_row_warp<VEC, CH, false, false>(P.f_ap, P.f_ai, P.f_ax, r, P.in0, P.n_cols, dst_row(r),
                                                  false, 0, 0, 0, lane);
@@ -220,11 +230,11 @@ __global__ void __launch_bounds__(kThreads, TF_MIN_CTAS) stream_kernel(const Par
     } else if (kind == 1) {
       // ---- consume: D[rb, re) = A * T ----
       if (re - rb == 1 && __ldg(P.s_ap + re) - __ldg(P.s_ap + rb) >= kHeavyNnz)
-        spmm_row_cta<VEC, CH, true, RING>(P.s_ap, P.s_ai, P.s_ax, rb, P.inter, P.n_cols,
+        spmm_row_cta<NT, VEC, CH, true, RING>(P.s_ap, P.s_ai, P.s_ax, rb, P.inter, P.n_cols,
                                           P.out + (size_t)rb * P.n_cols, P.relu != 0, base, P.ring_rows,
                                           P.m_local, sm.red);
       else {
-        const int q = (re - rb + kWarps - 1) / kWarps;
+        const int q = (re - rb + NW - 1) / NW;
         for (int r = rb + warp * q; r < min(re, rb + (warp + 1) * q); ++r)
           spmm_row_warp<VEC, CH, true, RING>(P.s_ap, P.s_ai, P.s_ax, r, P.inter, P.n_cols,
                                              P.out + (size_t)r * P.n_cols, P.relu != 0, base, P.ring_rows,
@@ -234,9 +244,29 @@ __global__ void __launch_bounds__(kThreads, TF_MIN_CTAS) stream_kernel(const Par
         __syncthreads();
         if (threadIdx.x == 0) publish(P.cons_done, block, P.epoch);
       }
-    } else {
+    } else if (TILED && kind == 4) {
+      // ---- produce the rows of one gather tile of the first operator ----
+      const int ring = RING ? P.ring_rows : 0;
+      auto dst_row = [&](int r) -> float * {
+        int t = r;
+        if (RING) { t = r - base; if (t >= ring) t -= ring; }
+        return P.inter + (size_t)t * P.n_cols;
+      };
+      tile_gather<false>(P.pt, rb, P.f_ap, P.f_ax, P.in0, P.n_cols, dst_row, false, 0, 0, 0, stage, hrow);
+      __syncthreads();
+      if (threadIdx.x == 0) publish(P.prod_done, block, P.epoch);
+    } else if (TILED && kind == 5) {
+      // ---- consume: the rows of one gather tile of the second operator ----
+      auto out_row = [&](int r) -> float * { return P.out + (size_t)r * P.n_cols; };
+      tile_gather<RING>(P.ct, rb, P.s_ap, P.s_ax, P.inter, P.n_cols, out_row, P.relu != 0, base, P.ring_rows,
+                        P.m_local, stage, hrow);
+      if (RING) {
+        __syncthreads();
+        if (threadIdx.x == 0) publish(P.cons_done, block, P.epoch);
+      }
+    } else if (kind == 2) {
       // ---- SDDMM-SpMM rows ----
-      for (int r = rb + warp; r < re; r += kWarps) sddmm_row_warp<VEC, CH>(P, r, lane);
+      for (int r = rb + warp; r < re; r += NW) sddmm_row_warp<VEC, CH>(P, r, lane);
     }
     __syncthreads();
     if (threadIdx.x == 0) s_next = nxt;
@@ -345,14 +375,15 @@ typedef void (*StreamFn)(const Params);
 typedef void (*SchedFn)(const Params, const SchedParams);
 
 template <int MODE, int VEC, int CH>
-static StreamFn pick_ring(bool ring) {
-  return ring ? stream_kernel<MODE, VEC, CH, true> : stream_kernel<MODE, VEC, CH, false>;
+static StreamFn pick_ring(bool ring, bool tiled) {
+  if (tiled) return ring ? stream_kernel<MODE, VEC, CH, true, true> : stream_kernel<MODE, VEC, CH, false, true>;
+  return ring ? stream_kernel<MODE, VEC, CH, true, false> : stream_kernel<MODE, VEC, CH, false, false>;
 }
 template <int MODE>
-static StreamFn pick_stream(int vec, int ch, bool ring) {
-  if (vec == 4) return ch == 2 ? pick_ring<MODE, 4, 2>(ring) : pick_ring<MODE, 4, 1>(ring);
-  if (vec == 2) return ch == 2 ? pick_ring<MODE, 2, 2>(ring) : pick_ring<MODE, 2, 1>(ring);
-  return ch == 2 ? pick_ring<MODE, 1, 2>(ring) : pick_ring<MODE, 1, 1>(ring);
+static StreamFn pick_stream(int vec, int ch, bool ring, bool tiled) {
+  if (vec == 4) return ch == 2 ? pick_ring<MODE, 4, 2>(ring, tiled) : pick_ring<MODE, 4, 1>(ring, tiled);
+  if (vec == 2) return ch == 2 ? pick_ring<MODE, 2, 2>(ring, false) : pick_ring<MODE, 2, 1>(ring, false);
+  return ch == 2 ? pick_ring<MODE, 1, 2>(ring, false) : pick_ring<MODE, 1, 1>(ring, false);
 }
 template <int MODE>
 static SchedFn pick_sched(int vec, int ch) {
@@ -367,23 +398,32 @@ void choose_shape(int n_cols, bool aligned16, int *vec, int *ch) {
   else { *vec = 1; *ch = n_cols > 32 ? 2 : 1; }
 }
 
-static StreamFn stream_fn(int mode, int vec, int ch, bool ring) {
+static StreamFn stream_fn(int mode, int vec, int ch, bool ring, bool tiled) {
   switch (mode) {
-    case 0: return pick_stream<0>(vec, ch, ring);
-    case 1: return pick_stream<1>(vec, ch, ring);
-    default: return pick_stream<2>(vec, ch, false);
+    case 0: return pick_stream<0>(vec, ch, ring, tiled);
+    case 1: return pick_stream<1>(vec, ch, ring, tiled);
+    default: return pick_stream<2>(vec, ch, false, false);
   }
 }
 
-int stream_occupancy(int mode, int vec, int ch, bool ring) {
+int stream_occupancy(int mode, int vec, int ch, bool ring, size_t dyn_smem) {
   int nb = 0;
-  cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, (const void *)stream_fn(mode, vec, ch, ring),
-                                                                kThreads, 0);
+  const void *fn = (const void *)stream_fn(mode, vec, ch, ring, dyn_smem > 0);
+  if (dyn_smem > 0 &&
+      cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem) != cudaSuccess)
+    return -1;
+  cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, dyn_smem > 0 ? kTiledThreads : kThreads, dyn_smem);
   return e == cudaSuccess ? nb : -1;
 }
 
-cudaError_t launch_stream(int mode, int vec, int ch, bool ring, int grid, const Params &p, cudaStream_t s) {
-  stream_fn(mode, vec, ch, ring)<<<grid, kThreads, 0, s>>>(p);
+cudaError_t launch_stream(int mode, int vec, int ch, bool ring, int grid, size_t dyn_smem, const Params &p,
+                          cudaStream_t s) {
+  StreamFn fn = stream_fn(mode, vec, ch, ring, dyn_smem > 0);
+  if (dyn_smem > 0) {
+    cudaError_t e = cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem);
+    if (e != cudaSuccess) return e;
+  }
+  fn<<<grid, dyn_smem > 0 ? kTiledThreads : kThreads, dyn_smem, s>>>(p);
   return cudaGetLastError();
 }
 

@@ -13,8 +13,9 @@
 
 namespace tfk {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 256;       // CTA size of the direct kernels
 constexpr int kWarps = kThreads / 32;
+constexpr int kTiledThreads = 512;  // CTA size of the gather-tile variant of the executor
 constexpr unsigned kFull = 0xffffffffu;
 
 struct ExecState {
@@ -24,6 +25,13 @@ struct ExecState {
   int finished;  // CTAs that left the item loop
   int error;     // sticky: a bounded wait ran out
   int pad[3];
+};
+
+// Gather tiles of one operator: tile -> output rows, tile -> staged source rows (slot order),
+// and per nonzero the slot its column occupies in the tile's staging buffer.
+struct TileArrays {
+  const int *row_ptr, *rows, *halo_ptr, *halo;
+  const unsigned short *slot;
 };
 
 struct Params {
@@ -48,6 +56,8 @@ struct Params {
   int relu, w_transposed;
   int reset_wm;      // last CTA clears the watermarks (last phase of a call)
   int spin_limit;    // polls before a wait gives up
+  TileArrays pt, ct; // gather tiles of the first / second operator (null when not tiled)
+  int tile_slots;    // staging slots per CTA (dynamic shared memory holds tile_slots * 132 bytes)
 };
 
 // ---------------------------------------------------------------------------
@@ -222,15 +232,16 @@ __device__ __forceinline__ void spmm_row_warp(const int *__restrict__ ap, const 
 
 // A row too heavy for one warp: the CTA's warps split its nonzeros and add their partial
 // sums through shared memory (panel by panel).
-template <int VEC, int CH, bool L2ONLY, bool RING>
+template <int NT, int VEC, int CH, bool L2ONLY, bool RING>
 __device__ __forceinline__ void spmm_row_cta(const int *__restrict__ ap, const int *__restrict__ ai,
                                              const float *__restrict__ ax, int row,
                                              const float *__restrict__ dense, int n_cols, float *out_row,
                                              bool relu, int base, int ring_rows, int m_local,
-                                             float *smem /* kWarps * 32*VEC*CH floats */) {
+                                             float *smem /* NT/32 * 32*VEC*CH floats */) {
+  constexpr int NW = NT / 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int p0 = __ldg(ap + row), p1 = __ldg(ap + row + 1);
-  const int per = ((p1 - p0 + kWarps - 1) / kWarps + 31) / 32 * 32;
+  const int per = ((p1 - p0 + NW - 1) / NW + 31) / 32 * 32;
   const int q0 = min(p1, p0 + warp * per), q1 = min(p1, q0 + per);
   constexpr int PANEL = 32 * VEC * CH;
   for (int col0 = 0; col0 < n_cols; col0 += PANEL) {
@@ -246,13 +257,124 @@ __device__ __forceinline__ void spmm_row_cta(const int *__restrict__ ap, const i
 #pragma unroll
       for (int i = 0; i < VEC; ++i) smem[warp * PANEL + (c * 32 + lane) * VEC + i] = acc[c][i];
     __syncthreads();
-    for (int t = threadIdx.x; t < PANEL; t += kThreads) {
+    for (int t = threadIdx.x; t < PANEL; t += NT) {
       float s = 0.f;
 #pragma unroll
-      for (int w = 0; w < kWarps; ++w) s += smem[w * PANEL + t];
+      for (int w = 0; w < NW; ++w) s += smem[w * PANEL + t];
       if (col0 + t < n_cols) out_row[col0 + t] = relu ? fmaxf(s, 0.f) : s;
     }
     __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Gather tile: out[r, :] = sum_p ax[p] * src[col_p, :] for the rows r of one tile.
+//
+// The dense source rows the tile needs are staged once per 32-column chunk (128 B per row) in
+// shared memory with 16-byte asynchronous copies that bypass L1, then every output row-chunk is
+// computed by 8 lanes (one float4 each) reading its operands from shared memory: a staged row is
+// fetched from L2 once and reused by every row of the tile that names it.  One warp works on four
+// rows at a time; a 128-byte slot is read by one quarter-warp, which is conflict-free.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+  const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// SRC_RING: source rows live in the ring (or after it, for halo rows).  dst_row(r) gives the
+// output row pointer.  A group of 8 lanes owns up to kTileRowsPerGroup rows of the tile; their row
+// ids, lengths and (slot, value) pairs -- lane k of the group holds nonzero k -- are loaded once
+// into registers and serve every column chunk, so the inner loop touches shared memory only.
+constexpr int kTileRowsPerGroup = 8;
+constexpr int kTileMaxRows = kTileRowsPerGroup * (kTiledThreads / 8);  // 512
+constexpr int kTileMaxSlots = 1700;  // staging slots a tile may use (shared-memory capacity)
+
+template <bool SRC_RING, class DstRow>
+__device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, const int *__restrict__ ap,
+                                            const float *__restrict__ ax, const float *__restrict__ src,
+                                            int n_cols, DstRow dst_row, bool relu, int base, int ring_rows,
+                                            int m_local, float4 *stage, int *hrow) {
+  const int rp = __ldg(ta.row_ptr + tile), nR = __ldg(ta.row_ptr + tile + 1) - rp;
+  const int hp = __ldg(ta.halo_ptr + tile), nH = __ldg(ta.halo_ptr + tile + 1) - hp;
+  const int g = threadIdx.x >> 3, l8 = threadIdx.x & 7;
+  int rr[kTileRowsPerGroup], cnt[kTileRowsPerGroup], ms[kTileRowsPerGroup];
+  float mv[kTileRowsPerGroup];
+#pragma unroll
+  for (int j = 0; j < kTileRowsPerGroup; ++j) {
+    const int i = j * (kTiledThreads / 8) + g;
+    rr[j] = -1; cnt[j] = 0; ms[j] = 0; mv[j] = 0.f;
+    if (i < nR) {
+      rr[j] = __ldg(ta.rows + rp + i);
+      const int p0 = __ldg(ap + rr[j]);
+      cnt[j] = __ldg(ap + rr[j] + 1) - p0;
+      if (l8 < cnt[j]) { ms[j] = __ldg(ta.slot + p0 + l8); mv[j] = __ldg(ax + p0 + l8); }
+    }
+  }
+  // source row of every slot, resolved once per tile: all loads are in flight together
+  __syncthreads();  // the previous tile's readers are done with hrow and the buffer
+  {
+    int v[kTileMaxSlots / kTiledThreads + 1];
+#pragma unroll
+    for (int u = 0; u < kTileMaxSlots / kTiledThreads + 1; ++u) {
+      const int s = threadIdx.x + u * kTiledThreads;
+      v[u] = s < nH ? __ldg(ta.halo + hp + s) : 0;
+    }
+#pragma unroll
+    for (int u = 0; u < kTileMaxSlots / kTiledThreads + 1; ++u) {
+      const int s = threadIdx.x + u * kTiledThreads;
+      if (s < nH) hrow[s] = map_row<SRC_RING>(v[u], base, ring_rows, m_local);
+    }
+  }
+  for (int c0 = 0; c0 < n_cols; c0 += 32) {
+    const int col = c0 + l8 * 4;
+    const bool col_ok = col < n_cols;
+    __syncthreads();  // hrow is complete; the previous chunk's readers are done with the buffer
+    if (col_ok)
+      for (int s = g; s < nH; s += kTiledThreads / 8)
+        cp_async16(stage + s * 8 + l8, src + (size_t)hrow[s] * n_cols + col);
+    cp_async_wait_all();
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kTileRowsPerGroup; ++j) {
+      if (j * (kTiledThreads / 8) >= nR) break;  // uniform over the CTA
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int sl = __shfl_sync(kFull, ms[j], k, 8);
+        const float v = __shfl_sync(kFull, mv[j], k, 8);
+        if (k < cnt[j] && col_ok) {
+          const float4 x = stage[sl * 8 + l8];
+          acc.x = fmaf(v, x.x, acc.x); acc.y = fmaf(v, x.y, acc.y);
+          acc.z = fmaf(v, x.z, acc.z); acc.w = fmaf(v, x.w, acc.w);
+        }
+      }
+      // rows with more than 8 nonzeros: the rest comes straight from the CSR arrays
+      const int longest = __reduce_max_sync(kFull, cnt[j]);
+      if (longest > 8) {
+        const int p0 = rr[j] >= 0 ? __ldg(ap + rr[j]) : 0;
+        for (int q = 8; q < longest; q += 8) {
+          int s2 = 0;
+          float v2 = 0.f;
+          if (q + l8 < cnt[j]) { s2 = __ldg(ta.slot + p0 + q + l8); v2 = __ldg(ax + p0 + q + l8); }
+          for (int k = 0; k < 8; ++k) {
+            const int sl = __shfl_sync(kFull, s2, k, 8);
+            const float v = __shfl_sync(kFull, v2, k, 8);
+            if (q + k < cnt[j] && col_ok) {
+              const float4 x = stage[sl * 8 + l8];
+              acc.x = fmaf(v, x.x, acc.x); acc.y = fmaf(v, x.y, acc.y);
+              acc.z = fmaf(v, x.z, acc.z); acc.w = fmaf(v, x.w, acc.w);
+            }
+          }
+        }
+      }
+      if (rr[j] >= 0 && col_ok) {
+        if (relu) { acc.x = fmaxf(acc.x, 0.f); acc.y = fmaxf(acc.y, 0.f); acc.z = fmaxf(acc.z, 0.f); acc.w = fmaxf(acc.w, 0.f); }
+        *reinterpret_cast<float4 *>(dst_row(rr[j]) + col) = acc;
+      }
+    }
   }
 }
 

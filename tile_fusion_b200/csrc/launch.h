@@ -10,8 +10,9 @@ struct Params;
 // vec = floats per lane (4, 2, 1), ch = vectors per lane (1, 2): column panel = 32*vec*ch.
 void choose_shape(int n_cols, bool aligned16, int *vec, int *ch);
 // mode: 0 SpMM-SpMM, 1 GeMM-SpMM, 2 SDDMM-SpMM
-int stream_occupancy(int mode, int vec, int ch, bool ring);
-cudaError_t launch_stream(int mode, int vec, int ch, bool ring, int grid, const Params &p, cudaStream_t s);
+int stream_occupancy(int mode, int vec, int ch, bool ring, size_t dyn_smem);
+cudaError_t launch_stream(int mode, int vec, int ch, bool ring, int grid, size_t dyn_smem, const Params &p,
+                          cudaStream_t s);
 cudaError_t launch_schedule_level(int mode, int vec, int ch, int grid, const Params &p, const int *ptr2,
                                   const int *id, const int *type, const int *ker, int part_begin, int part_end,
                                   cudaStream_t s);

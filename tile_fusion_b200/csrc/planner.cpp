@@ -46,103 +46,127 @@ inline int block_of(const std::vector<int> &bounds, int row) {
 }  // namespace
 
 int build_stream_plan(const PlanParams &pp, const int *first_ap, const int * /*first_ai*/, const int *sec_ap,
-                      const int *sec_ai, HostPlan &out) {
+                      const int *sec_ai, const Tiling *ptile, const Tiling *ctile, HostPlan &out) {
   const int m = pp.m;
   const int rb = pp.rows_per_block;
-  out.prod_rows = split_rows(m, pp.producer_is_gemm ? nullptr : first_ap, rb, pp.max_block_nnz);
-  out.cons_rows = split_rows(m, sec_ap, rb, pp.max_block_nnz);
-  const int np = (int)out.prod_rows.size() - 1, nc = (int)out.cons_rows.size() - 1;
+  const bool p_tiled = ptile && ptile->tiled, c_tiled = ctile && ctile->tiled;
 
-  // column window of every consumer block, local columns only (columns >= m are halo rows)
-  std::vector<int> cmin(nc, INT_MAX), cmax(nc, -1);
-  std::vector<char> halo(nc, 0);
-  for (int c = 0; c < nc; ++c)
-    for (int r = out.cons_rows[c]; r < out.cons_rows[c + 1]; ++r)
-      for (int j = sec_ap[r]; j < sec_ap[r + 1]; ++j) {
-        const int col = sec_ai[j];
-        if (col >= m) { halo[c] = 1; continue; }
-        cmin[c] = std::min(cmin[c], col);
-        cmax[c] = std::max(cmax[c], col);
+  // ---- units: gather tiles where the operator is tiled, consecutive row blocks otherwise ----
+  out.prod_rows.clear();
+  out.cons_rows.clear();
+  if (!p_tiled) out.prod_rows = split_rows(m, pp.producer_is_gemm ? nullptr : first_ap, rb, pp.max_block_nnz);
+  if (!c_tiled) out.cons_rows = split_rows(m, sec_ap, rb, pp.max_block_nnz);
+  const int np = p_tiled ? ptile->tiles() : (int)out.prod_rows.size() - 1;
+  const int nc = c_tiled ? ctile->tiles() : (int)out.cons_rows.size() - 1;
+  out.n_prod = np;
+  out.n_cons = nc;
+
+  std::vector<int> prod_of_row((size_t)m, 0), pmin(np, INT_MAX), pmax(np, -1);
+  for (int j = 0; j < np; ++j) {
+    if (p_tiled) {
+      for (int k = ptile->tile_row_ptr[j]; k < ptile->tile_row_ptr[j + 1]; ++k) {
+        const int r = ptile->rows[k];
+        prod_of_row[r] = j; pmin[j] = std::min(pmin[j], r); pmax[j] = std::max(pmax[j], r);
       }
-  // monotone closure so that one contiguous watermark per side expresses every dependence
-  std::vector<int> emax(nc), emin(nc);
-  for (int c = 0, run = -1; c < nc; ++c) { run = std::max(run, cmax[c]); emax[c] = run; }
-  for (int c = nc - 1, run = INT_MAX; c >= 0; --c) { run = std::min(run, cmin[c]); emin[c] = run; }
-  std::vector<int> need(nc);  // producer blocks that must be complete
-  for (int c = 0; c < nc; ++c) need[c] = emax[c] < 0 ? 0 : block_of(out.prod_rows, emax[c]) + 1;
+    } else {
+      for (int r = out.prod_rows[j]; r < out.prod_rows[j + 1]; ++r) prod_of_row[r] = j;
+      pmin[j] = out.prod_rows[j]; pmax[j] = out.prod_rows[j + 1] - 1;
+    }
+  }
+  // what every consumer unit reads: lowest / highest local row, last producer unit, any halo row
+  std::vector<int> cmin(nc, INT_MAX), cmax(nc, -1), need(nc, 0);
+  std::vector<char> halo(nc, 0);
+  auto see = [&](int c, int col) {
+    if (col >= m) { halo[c] = 1; return; }
+    cmin[c] = std::min(cmin[c], col);
+    cmax[c] = std::max(cmax[c], col);
+    need[c] = std::max(need[c], prod_of_row[col] + 1);
+  };
+  for (int c = 0; c < nc; ++c) {
+    if (c_tiled) {
+      for (int k = ctile->tile_halo_ptr[c]; k < ctile->tile_halo_ptr[c + 1]; ++k) see(c, ctile->halo[k]);
+    } else {
+      for (int r = out.cons_rows[c]; r < out.cons_rows[c + 1]; ++r)
+        for (int j = sec_ap[r]; j < sec_ap[r + 1]; ++j) see(c, sec_ai[j]);
+    }
+  }
 
   int slack = pp.slack_blocks >= 0 ? pp.slack_blocks : std::max(1, pp.max_ctas / 2);
   slack = std::min(slack, np);
-  int max_block = 1;
-  for (int p = 0; p < np; ++p) max_block = std::max(max_block, out.prod_rows[p + 1] - out.prod_rows[p]);
-
-  // widest live window in rows: from the lowest row any not-yet-finished consumer still reads to the
-  // highest row produced when that consumer's ticket comes up
-  long long span = 0;
-  for (int c = 0; c < nc; ++c) {
-    if (emax[c] < 0) continue;
-    const int hi_block = std::min(np, need[c] + slack);
-    const long long hi_row = out.prod_rows[hi_block];
-    const long long lo_row = std::min<long long>(emin[c] == INT_MAX ? hi_row : emin[c], hi_row);
-    span = std::max(span, hi_row - lo_row);
-  }
   const bool multi = pp.halo_rows > 0 || !pp.boundary_rows.empty();
+
+  // ---- ticket order: a consumer is listed once `slack` producers beyond its last need are listed ----
+  struct Entry { int is_cons, idx, cons_before; };
+  std::vector<Entry> order;
+  order.reserve((size_t)np + nc);
+  std::vector<int> late;
+  {
+    int pi = 0, ci = 0;
+    while (pi < np || ci < nc) {
+      while (ci < nc && halo[ci] && multi) { late.push_back(ci); ++ci; }
+      if (ci >= nc && pi >= np) break;
+      if (ci < nc && pi >= std::min(np, need[ci] + slack)) { order.push_back({1, ci, ci}); ++ci; }
+      else if (pi < np) { order.push_back({0, pi, ci}); ++pi; }
+      else { order.push_back({1, ci, ci}); ++ci; }
+    }
+  }
+  // lowest row still to be read by consumer c or any later one (halo consumers never read the ring)
+  std::vector<int> sufmin((size_t)nc + 1, INT_MAX);
+  for (int c = nc - 1; c >= 0; --c) sufmin[c] = std::min(sufmin[c + 1], (multi && halo[c]) ? INT_MAX : cmin[c]);
+
+  // ---- ring: large enough that a producer never overwrites a row a listed-later consumer reads ----
   long long ring_rows = 0;
   if (pp.ring_bytes > 0 && !multi) {
-    // producers run up to `slack` blocks past the window before they have to wait
-    long long want = span + (long long)(slack + 2) * max_block;
-    want = (want + 7) / 8 * 8;
+    // A producer should find its slot free without waiting: count as finished only the consumers
+    // listed at least `lag` tickets before it (about one ticket per resident CTA).
+    const int lag = 2 * slack + 2;
+    long long live = 0;
+    for (size_t q = 0; q < order.size(); ++q) {
+      const Entry &e = order[q];
+      if (e.is_cons) continue;
+      live = std::max<long long>(live, (long long)pmax[e.idx] - pmin[e.idx] + 1);
+      const int done_before = q >= (size_t)lag ? order[q - lag].cons_before : 0;
+      if (sufmin[done_before] != INT_MAX && sufmin[done_before] <= pmax[e.idx])
+        live = std::max<long long>(live, (long long)pmax[e.idx] - sufmin[done_before] + 1);
+    }
+    for (int c = 0; c < nc; ++c)
+      if (cmax[c] >= 0) live = std::max<long long>(live, (long long)cmax[c] - cmin[c] + 1);
+    const long long want = (live + 1 + 7) / 8 * 8;
     if (want * pp.n_cols * 4LL <= pp.ring_bytes && want < m) ring_rows = want;
   }
   out.ring_rows = ring_rows;
   out.inter_rows = ring_rows ? ring_rows : (long long)m + pp.halo_rows;
 
-  // consumers a producer must see finished before it may overwrite its ring slot
-  auto cons_before = [&](int p) -> int {
-    if (!ring_rows) return 0;
-    const long long x = (long long)out.prod_rows[p + 1] - 1 - ring_rows;  // highest old row in the slot
-    if (x < 0) return 0;
-    // consumers c with emin[c] <= x still read rows at or below x; emin is non-decreasing
-    int lo = 0, hi = nc;
-    while (lo < hi) { int mid = (lo + hi) / 2; if (emin[mid] <= x) lo = mid + 1; else hi = mid; }
-    return lo;
-  };
-
   out.items.clear();
-  out.phase_begin[0] = 0;
-  out.phase_begin[1] = 0;  // phase 0 (boundary rows) is a row-list kernel, not items
-  int pi = 0, ci = 0;
-  std::vector<int> late;  // consumers that read halo rows
+  out.phase_begin[0] = out.phase_begin[1] = 0;
   auto emit_cons = [&](int c) {
     Item it{};
-    it.kind = ITEM_CONSUME; it.block = c;
-    it.row_begin = out.cons_rows[c]; it.row_end = out.cons_rows[c + 1];
+    it.kind = c_tiled ? ITEM_CONSUME_TILED : ITEM_CONSUME;
+    it.block = c;
+    it.row_begin = c_tiled ? c : out.cons_rows[c];
+    it.row_end = c_tiled ? c + 1 : out.cons_rows[c + 1];
     it.need = need[c];
-    it.base = 0;
-    if (ring_rows && emin[c] != INT_MAX) it.base = (int)((emin[c] / ring_rows) * ring_rows);
+    it.base = (ring_rows && cmin[c] != INT_MAX) ? (int)((cmin[c] / ring_rows) * ring_rows) : 0;
     out.items.push_back(it);
   };
-  while (pi < np || ci < nc) {
-    while (ci < nc && halo[ci] && multi) { late.push_back(ci); ++ci; }
-    if (ci >= nc && pi >= np) break;
-    const bool cons_ready = ci < nc && pi >= std::min(np, need[ci] + slack);
-    if (cons_ready) { emit_cons(ci); ++ci; continue; }
-    if (pi < np) {
-      const int cb = cons_before(pi);
-      if (cb > ci) {
-        // ring too small for this ordering: should not happen given how ring_rows was sized
-        return fail(TF_ERR_UNSUPPORTED, "planner: ring dependence cycle (internal sizing error)");
-      }
-      Item it{};
-      it.kind = ITEM_PRODUCE; it.block = pi;
-      it.row_begin = out.prod_rows[pi]; it.row_end = out.prod_rows[pi + 1];
-      it.need = cb;
-      out.items.push_back(it);
-      ++pi;
-      continue;
+  for (const Entry &e : order) {
+    if (e.is_cons) { emit_cons(e.idx); continue; }
+    const int j = e.idx;
+    Item it{};
+    it.kind = p_tiled ? ITEM_PRODUCE_TILED : ITEM_PRODUCE;
+    it.block = j;
+    it.row_begin = p_tiled ? j : out.prod_rows[j];
+    it.row_end = p_tiled ? j + 1 : out.prod_rows[j + 1];
+    it.base = ring_rows ? (int)((pmin[j] / ring_rows) * ring_rows) : 0;
+    if (ring_rows) {
+      // consumers that still read the rows this unit overwrites: those with sufmin <= pmax - ring
+      const long long x = (long long)pmax[j] - ring_rows;
+      int lo = 0, hi = nc;
+      while (lo < hi) { const int mid = (lo + hi) / 2; if (sufmin[mid] <= x) lo = mid + 1; else hi = mid; }
+      it.need = x < 0 ? 0 : lo;
+      if (it.need > e.cons_before) return fail(TF_ERR_UNSUPPORTED, "planner: ring dependence cycle (internal sizing error)");
     }
-    // only consumers left and all producers are listed
-    emit_cons(ci); ++ci;
+    out.items.push_back(it);
   }
   out.phase_begin[2] = (int)out.items.size();
   for (int c : late) emit_cons(c);
@@ -154,6 +178,8 @@ int build_single_pass_plan(const PlanParams &pp, const int *ap, HostPlan &out) {
   out.prod_rows.clear();
   out.cons_rows = split_rows(pp.m, ap, pp.rows_per_block, pp.max_block_nnz);
   const int nc = (int)out.cons_rows.size() - 1;
+  out.n_prod = 0;
+  out.n_cons = nc;
   out.items.clear();
   for (int c = 0; c < nc; ++c) {
     Item it{};
@@ -189,7 +215,13 @@ extern "C" int tf_plan_preview(const tf_csr *A, const tf_csr *B, int producer_is
   if (o && o->mode == TF_MODE_UNFUSED) { pp.slack_blocks = 1 << 30; pp.ring_bytes = -1; }
   const tf_csr *F = producer_is_gemm ? nullptr : (B ? B : A);
   tf::HostPlan hp;
-  int rc = tf::build_stream_plan(pp, F ? F->ap : nullptr, F ? F->ai : nullptr, A->ap, A->ai, hp);
+  tf::Tiling pt, ct;
+  const int cap = (!o || o->tile_slots == 0) ? tf::kDefaultTileSlots : o->tile_slots;
+  if (cap > 0 && n_cols % 4 == 0 && !(o && o->mode == TF_MODE_SCHEDULE)) {
+    if (F) tf::build_tiling(F->m, F->ap, F->ai, cap, (o && o->tile_max_bz > 0) ? o->tile_max_bz : tf::kDefaultTileMaxBz, pt);
+    tf::build_tiling(A->m, A->ap, A->ai, cap, (o && o->tile_max_bz > 0) ? o->tile_max_bz : tf::kDefaultTileMaxBz, ct);
+  }
+  int rc = tf::build_stream_plan(pp, F ? F->ap : nullptr, F ? F->ai : nullptr, A->ap, A->ai, &pt, &ct, hp);
   if (rc != TF_OK) return rc;
   int *buf = (int *)malloc(sizeof(int) * 8 * std::max<size_t>(hp.items.size(), 1));
   if (!buf) return tf::fail(TF_ERR_NOMEM, "tf_plan_preview: out of memory");
@@ -202,8 +234,8 @@ extern "C" int tf_plan_preview(const tf_csr *A, const tf_csr *B, int producer_is
   *items_out = buf;
   *n_items = (long long)hp.items.size();
   info[0] = (long long)hp.items.size();
-  info[1] = (long long)hp.prod_rows.size() - 1;
-  info[2] = (long long)hp.cons_rows.size() - 1;
+  info[1] = hp.n_prod;
+  info[2] = hp.n_cons;
   info[3] = hp.ring_rows;
   info[4] = hp.phase_begin[1]; info[5] = hp.phase_begin[2]; info[6] = hp.phase_begin[3];
   info[7] = hp.inter_rows;
@@ -211,3 +243,22 @@ extern "C" int tf_plan_preview(const tf_csr *A, const tf_csr *B, int producer_is
 }
 
 extern "C" void tf_free(void *p) { free(p); }
+
+// Host-only view of the gather tiles the library would build for an operator.
+extern "C" int tf_tiling_preview(const tf_csr *A, int tile_slots, int tile_max_bz, int **row_ptr, int **rows,
+                                 int **halo_ptr, int **halo, int *n_tiles, int info[4]) {
+  if (!A || !row_ptr || !rows || !halo_ptr || !halo || !n_tiles || !info)
+    return tf::fail(TF_ERR_ARG, "tf_tiling_preview: null argument");
+  tf::Tiling t;
+  const int cap = tile_slots == 0 ? tf::kDefaultTileSlots : tile_slots;
+  if (cap > 0) tf::build_tiling(A->m, A->ap, A->ai, cap, tile_max_bz > 0 ? tile_max_bz : tf::kDefaultTileMaxBz, t);
+  *n_tiles = t.tiled ? t.tiles() : 0;
+  info[0] = t.bx; info[1] = t.by; info[2] = t.bz; info[3] = (int)(t.reuse * 1000);
+  auto dup = [](const std::vector<int> &v) {
+    int *b = (int *)malloc(sizeof(int) * std::max<size_t>(v.size(), 1));
+    if (b && !v.empty()) std::copy(v.begin(), v.end(), b);
+    return b;
+  };
+  *row_ptr = dup(t.tile_row_ptr); *rows = dup(t.rows); *halo_ptr = dup(t.tile_halo_ptr); *halo = dup(t.halo);
+  return TF_OK;
+}

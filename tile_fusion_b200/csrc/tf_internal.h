@@ -15,11 +15,19 @@ struct tf_schedule {
 
 namespace tf {
 
+constexpr int kDefaultTileSlots = 800;  // 100 KB of staging per CTA: two CTAs per SM
+constexpr int kDefaultTileMaxBz = 8;
+constexpr int kTileMaxRows = 512;        // rows of a gather tile (16 per 8-lane group of a 256-thread CTA)
+
 void set_error(const std::string &msg);
 int fail(int code, const std::string &msg);
 
 // Work item of the persistent executor (two int4 on the device).
-enum ItemKind : int { ITEM_PRODUCE = 0, ITEM_CONSUME = 1, ITEM_SDDMM = 2 };
+enum ItemKind : int {
+  ITEM_PRODUCE = 0, ITEM_CONSUME = 1, ITEM_SDDMM = 2, ITEM_SEND = 3,
+  ITEM_PRODUCE_TILED = 4,  // row_begin = tile index of the first operator's tiling
+  ITEM_CONSUME_TILED = 5   // row_begin = tile index of the second operator's tiling
+};
 struct Item {
   int kind;       // ItemKind
   int block;      // index into the producer / consumer done-flag array
@@ -30,10 +38,23 @@ struct Item {
   int aux0, aux1;
 };
 
+// Partition of an operator's rows into gather tiles (see tiling.cpp).
+struct Tiling {
+  bool tiled = false, failed = false;
+  int nx = 0, ny = 0, bx = 0, by = 0, bz = 0;
+  std::vector<int> tile_row_ptr, rows;    // tile -> its output rows
+  std::vector<int> tile_halo_ptr, halo;   // tile -> the source rows it stages, in slot order
+  std::vector<uint16_t> slot;             // per nonzero of the operator: slot of its column in the tile
+  double reuse = 0;                       // nonzeros per staged row
+  int tiles() const { return tile_row_ptr.empty() ? 0 : (int)tile_row_ptr.size() - 1; }
+};
+int build_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_bz, Tiling &out);
+
 // Host-side execution plan (what the planner derives from the patterns).
 struct HostPlan {
-  std::vector<int> prod_rows;  // producer block boundaries (size blocks + 1)
-  std::vector<int> cons_rows;  // consumer block boundaries
+  std::vector<int> prod_rows;  // producer block boundaries (size blocks + 1); empty when tiled
+  std::vector<int> cons_rows;  // consumer block boundaries; empty when tiled
+  int n_prod = 0, n_cons = 0;  // units (blocks or tiles) on each side
   std::vector<Item> items;     // all items in ticket order
   int phase_begin[4] = {0, 0, 0, 0};  // item ranges of the three phases
   long long ring_rows = 0;     // 0 = intermediate holds every row
@@ -55,7 +76,7 @@ struct PlanParams {
 
 // first: CSR pattern of the first operator (nullptr for a dense producer); second: of A.
 int build_stream_plan(const PlanParams &pp, const int *first_ap, const int *first_ai, const int *sec_ap,
-                      const int *sec_ai, HostPlan &out);
+                      const int *sec_ai, const Tiling *ptile, const Tiling *ctile, HostPlan &out);
 int build_single_pass_plan(const PlanParams &pp, const int *ap, HostPlan &out);
 
 int check_csr(int m, int ncols, const int *ap, const int *ai, bool need_sorted);
