@@ -218,6 +218,30 @@ int tf_sddmm_spmm_host(tf_plan *p, const float *Q, const float *K, const float *
 int tf_spmm_dev(const int *Ap, const int *Ai, const float *Ax, int m, const float *X, int n_cols,
                 float *out, void *stream);
 
+/* SpMM-SpMM, D = A * (A * C), for callers that cannot allocate device memory.
+ *
+ * Has no counterpart in the reference.  It is meant for host code that is not allowed to call
+ * cudaMalloc / cudaFree at the point where it needs the product: those calls take the driver's
+ * allocator lock and may synchronise the whole device, which a request loop that has finished its
+ * warm-up, or a component living under somebody else's memory-pool policy, cannot afford.  This
+ * entry point therefore calls no allocating routine at all: A (m x m CSR), C and D (m x n_cols,
+ * row-major) are DEVICE pointers the caller already owns, and the intermediate A*C is kept in an
+ * array that is part of the library image -- tf_noalloc_max_floats() floats (4 Mi = 16 MiB),
+ * resident on every GPU that loads the library until the process ends.
+ *
+ * Limits and rules:
+ *  - m * n_cols must not exceed tf_noalloc_max_floats(); larger problems get TF_ERR_ARG with a
+ *    message naming the limit (use a plan instead).
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current) and remembers it; make that first call before any stream capture begins.
+ *  - All calls share the one array and it keeps whatever the last call left there.  Each call
+ *    rewrites every row it later reads, so nothing needs clearing, but two calls whose kernels
+ *    overlap on the GPU (different streams, no ordering between them) race on it.
+ *  - Work is enqueued on `stream` (cudaStream_t, NULL = default); the call does not wait for it.  */
+int tf_spmm_spmm_noalloc(const int *Ap, const int *Ai, const float *Ax, int m, const float *C, int n_cols,
+                         float *D, void *stream);
+long long tf_noalloc_max_floats(void);
+
 /* Counter-based seeded fills on the device: uniform[-1,1) is bit-identical to the host
  * generator, N(0, sigma^2) (Box-Muller) agrees with it to float rounding of log/cos;
  * `offset` is the index of the first element. */

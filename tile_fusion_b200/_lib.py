@@ -42,7 +42,8 @@ EXPORTS = [
     "tf_schedule_free", "tf_plan_spmm_spmm", "tf_plan_gemm_spmm", "tf_plan_sddmm_spmm", "tf_plan_free",
     "tf_plan_info", "tf_plan_status", "tf_exec_spmm_spmm", "tf_exec_gemm_spmm", "tf_exec_sddmm_spmm",
     "tf_exec_phase", "tf_plan_intermediate", "tf_plan_exchange_buffers", "tf_spmm_spmm_host", "tf_gemm_spmm_host",
-    "tf_sddmm_spmm_host", "tf_spmm_dev", "tf_fill_uniform", "tf_fill_normal", "tf_plan_preview", "tf_free", "tf_plan_set_wait_limit", "tf_tiling_preview", "tf_plan_tile_info",
+    "tf_sddmm_spmm_host", "tf_spmm_dev", "tf_fill_uniform", "tf_fill_normal", "tf_plan_preview", "tf_free", "tf_plan_set_wait_limit", "tf_tiling_preview", "tf_plan_tile_info", "tf_spmm_spmm_noalloc",
+    "tf_noalloc_max_floats",
 ]
 
 _lib = None
@@ -96,6 +97,8 @@ def lib() -> C.CDLL:
     L.tf_plan_set_wait_limit.argtypes = [vp, i]
     L.tf_tiling_preview.argtypes = [C.POINTER(Csr), i, i] + [C.POINTER(vp)] * 4 + [ip, ip]
     L.tf_plan_tile_info.argtypes = [vp, ip]
+    L.tf_spmm_spmm_noalloc.argtypes = [vp, vp, vp, i, vp, i, vp, vp]
+    L.tf_noalloc_max_floats.restype = C.c_longlong
     L.tf_free.restype = None
     _lib = L
     return L
