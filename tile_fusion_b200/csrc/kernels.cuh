@@ -285,11 +285,15 @@ __device__ __forceinline__ void cp_async_wait_all() {
 }
 
 // SRC_RING: source rows live in the ring (or after it, for halo rows).  dst_row(r) gives the
-// output row pointer.  A group of 8 lanes owns up to kTileRowsPerGroup rows of the tile; their row
-// ids, lengths and (slot, value) pairs -- lane k of the group holds nonzero k -- are loaded once
-// into registers and serve every column chunk, so the inner loop touches shared memory only.
-constexpr int kTileRowsPerGroup = 8;
-constexpr int kTileMaxRows = kTileRowsPerGroup * (kTiledThreads / 8);  // 512
+// output row pointer.  A group of 4 lanes owns up to kTileRowsPerGroup rows of the tile and computes
+// each row's 32-column chunk as two float4 per lane; their row ids, lengths and (slot, value) pairs
+// -- lane l of the group holds nonzeros l and l + 4 -- are loaded once into registers and serve every
+// column chunk, so the inner loop touches shared memory only.  The two groups that share a
+// quarter-warp read opposite 64-byte halves of their slots in each load, which keeps the 128-bit
+// shared loads conflict-free.
+constexpr int kTileGroups = kTiledThreads / 4;                     // 128 groups of 4 lanes
+constexpr int kTileRowsPerGroup = 4;
+constexpr int kTileMaxRows = kTileRowsPerGroup * kTileGroups;      // 512
 constexpr int kTileMaxSlots = 1700;  // staging slots a tile may use (shared-memory capacity)
 
 template <bool SRC_RING, class DstRow>
@@ -299,20 +303,35 @@ __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, cons
                                             int m_local, float4 *stage, int *hrow) {
   const int rp = __ldg(ta.row_ptr + tile), nR = __ldg(ta.row_ptr + tile + 1) - rp;
   const int hp = __ldg(ta.halo_ptr + tile), nH = __ldg(ta.halo_ptr + tile + 1) - hp;
-  const int g = threadIdx.x >> 3, l8 = threadIdx.x & 7;
-  int rr[kTileRowsPerGroup], cnt[kTileRowsPerGroup], ms[kTileRowsPerGroup];
-  float mv[kTileRowsPerGroup];
+  const int g8 = threadIdx.x >> 3, l8 = threadIdx.x & 7;  // staging: 8 lanes per 128-byte slot
+  const int g4 = threadIdx.x >> 2, l4 = threadIdx.x & 3;  // compute: 4 lanes per row
+  const int colA = ((g4 & 1) * 16) + l4 * 4, colB = (((g4 & 1) ^ 1) * 16) + l4 * 4;  // floats within the chunk
+  const char *sA = reinterpret_cast<const char *>(stage) + colA * 4;
+  const char *sB = reinterpret_cast<const char *>(stage) + colB * 4;
+  int rr[kTileRowsPerGroup], cnt[kTileRowsPerGroup], ms[kTileRowsPerGroup][2];
+  float mv[kTileRowsPerGroup][2];
+  int wmax = 0;
 #pragma unroll
   for (int j = 0; j < kTileRowsPerGroup; ++j) {
-    const int i = j * (kTiledThreads / 8) + g;
-    rr[j] = -1; cnt[j] = 0; ms[j] = 0; mv[j] = 0.f;
+    const int i = j * kTileGroups + g4;
+    rr[j] = -1; cnt[j] = 0;
+    ms[j][0] = ms[j][1] = 0; mv[j][0] = mv[j][1] = 0.f;
     if (i < nR) {
       rr[j] = __ldg(ta.rows + rp + i);
       const int p0 = __ldg(ap + rr[j]);
       cnt[j] = __ldg(ap + rr[j] + 1) - p0;
-      if (l8 < cnt[j]) { ms[j] = __ldg(ta.slot + p0 + l8); mv[j] = __ldg(ax + p0 + l8); }
+      // slots are kept as byte offsets into the staging buffer; padding names slot 0 with value 0
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        if (l4 + 4 * h < cnt[j]) {
+          ms[j][h] = (int)__ldg(ta.slot + p0 + l4 + 4 * h) * 128;
+          mv[j][h] = __ldg(ax + p0 + l4 + 4 * h);
+        }
     }
+    wmax = max(wmax, cnt[j]);
   }
+  wmax = __reduce_max_sync(kFull, wmax);  // longest row this warp owns
+  const int kshort = min(wmax, 8);
   // source row of every slot, resolved once per tile: all loads are in flight together
   __syncthreads();  // the previous tile's readers are done with hrow and the buffer
   {
@@ -329,50 +348,57 @@ __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, cons
     }
   }
   for (int c0 = 0; c0 < n_cols; c0 += 32) {
-    const int col = c0 + l8 * 4;
-    const bool col_ok = col < n_cols;
     __syncthreads();  // hrow is complete; the previous chunk's readers are done with the buffer
-    if (col_ok)
-      for (int s = g; s < nH; s += kTiledThreads / 8)
-        cp_async16(stage + s * 8 + l8, src + (size_t)hrow[s] * n_cols + col);
+    if (c0 + l8 * 4 < n_cols)
+      for (int s = g8; s < nH; s += kTiledThreads / 8)
+        cp_async16(stage + s * 8 + l8, src + (size_t)hrow[s] * n_cols + c0 + l8 * 4);
     cp_async_wait_all();
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < kTileRowsPerGroup; ++j) {
-      if (j * (kTiledThreads / 8) >= nR) break;  // uniform over the CTA
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j * kTileGroups >= nR) break;  // uniform over the CTA
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const int sl = __shfl_sync(kFull, ms[j], k, 8);
-        const float v = __shfl_sync(kFull, mv[j], k, 8);
-        if (k < cnt[j] && col_ok) {
-          const float4 x = stage[sl * 8 + l8];
-          acc.x = fmaf(v, x.x, acc.x); acc.y = fmaf(v, x.y, acc.y);
-          acc.z = fmaf(v, x.z, acc.z); acc.w = fmaf(v, x.w, acc.w);
+        if (k < kshort) {  // uniform over the warp
+          const int off = __shfl_sync(kFull, ms[j][k >> 2], k & 3, 4);
+          const float v = __shfl_sync(kFull, mv[j][k >> 2], k & 3, 4);
+          const float4 x = *reinterpret_cast<const float4 *>(sA + off);
+          const float4 y = *reinterpret_cast<const float4 *>(sB + off);
+          if (k < cnt[j]) {
+            a.x = fmaf(v, x.x, a.x); a.y = fmaf(v, x.y, a.y); a.z = fmaf(v, x.z, a.z); a.w = fmaf(v, x.w, a.w);
+            b.x = fmaf(v, y.x, b.x); b.y = fmaf(v, y.y, b.y); b.z = fmaf(v, y.z, b.z); b.w = fmaf(v, y.w, b.w);
+          }
         }
       }
       // rows with more than 8 nonzeros: the rest comes straight from the CSR arrays
-      const int longest = __reduce_max_sync(kFull, cnt[j]);
-      if (longest > 8) {
+      if (wmax > 8) {
+        const int longest = __reduce_max_sync(kFull, cnt[j]);
         const int p0 = rr[j] >= 0 ? __ldg(ap + rr[j]) : 0;
-        for (int q = 8; q < longest; q += 8) {
+        for (int q = 8; q < longest; q += 4) {
           int s2 = 0;
           float v2 = 0.f;
-          if (q + l8 < cnt[j]) { s2 = __ldg(ta.slot + p0 + q + l8); v2 = __ldg(ax + p0 + q + l8); }
-          for (int k = 0; k < 8; ++k) {
-            const int sl = __shfl_sync(kFull, s2, k, 8);
-            const float v = __shfl_sync(kFull, v2, k, 8);
-            if (q + k < cnt[j] && col_ok) {
-              const float4 x = stage[sl * 8 + l8];
-              acc.x = fmaf(v, x.x, acc.x); acc.y = fmaf(v, x.y, acc.y);
-              acc.z = fmaf(v, x.z, acc.z); acc.w = fmaf(v, x.w, acc.w);
+          if (q + l4 < cnt[j]) { s2 = (int)__ldg(ta.slot + p0 + q + l4) * 128; v2 = __ldg(ax + p0 + q + l4); }
+          for (int k = 0; k < 4; ++k) {
+            const int off = __shfl_sync(kFull, s2, k, 4);
+            const float v = __shfl_sync(kFull, v2, k, 4);
+            const float4 x = *reinterpret_cast<const float4 *>(sA + off);
+            const float4 y = *reinterpret_cast<const float4 *>(sB + off);
+            if (q + k < cnt[j]) {
+              a.x = fmaf(v, x.x, a.x); a.y = fmaf(v, x.y, a.y); a.z = fmaf(v, x.z, a.z); a.w = fmaf(v, x.w, a.w);
+              b.x = fmaf(v, y.x, b.x); b.y = fmaf(v, y.y, b.y); b.z = fmaf(v, y.z, b.z); b.w = fmaf(v, y.w, b.w);
             }
           }
         }
       }
-      if (rr[j] >= 0 && col_ok) {
-        if (relu) { acc.x = fmaxf(acc.x, 0.f); acc.y = fmaxf(acc.y, 0.f); acc.z = fmaxf(acc.z, 0.f); acc.w = fmaxf(acc.w, 0.f); }
-        *reinterpret_cast<float4 *>(dst_row(rr[j]) + col) = acc;
+      if (rr[j] >= 0) {
+        if (relu) {
+          a.x = fmaxf(a.x, 0.f); a.y = fmaxf(a.y, 0.f); a.z = fmaxf(a.z, 0.f); a.w = fmaxf(a.w, 0.f);
+          b.x = fmaxf(b.x, 0.f); b.y = fmaxf(b.y, 0.f); b.z = fmaxf(b.z, 0.f); b.w = fmaxf(b.w, 0.f);
+        }
+        float *o = dst_row(rr[j]) + c0;
+        if (c0 + colA < n_cols) *reinterpret_cast<float4 *>(o + colA) = a;
+        if (c0 + colB < n_cols) *reinterpret_cast<float4 *>(o + colB) = b;
       }
     }
   }

@@ -91,7 +91,8 @@ int build_stream_plan(const PlanParams &pp, const int *first_ap, const int * /*f
     }
   }
 
-  int slack = pp.slack_blocks >= 0 ? pp.slack_blocks : std::max(1, pp.max_ctas / 2);
+  // every resident CTA holds the item it works on and the next ticket, about half of them producers
+  int slack = pp.slack_blocks >= 0 ? pp.slack_blocks : std::max(1, pp.max_ctas + 8);
   slack = std::min(slack, np);
   const bool multi = pp.halo_rows > 0 || !pp.boundary_rows.empty();
 
