@@ -218,6 +218,12 @@ int tf_sddmm_spmm_host(tf_plan *p, const float *Q, const float *K, const float *
 int tf_spmm_dev(const int *Ap, const int *Ai, const float *Ax, int m, const float *X, int n_cols,
                 float *out, void *stream);
 
+/* The dense producer alone: T = B * W on device pointers, B m x K, W K x N (N x K when w_transposed),
+ * on the tcgen05 tensor cores with the 3xTF32 split (fp32 accuracy).  Needs K % 4 == 0, N % 16 == 0,
+ * N <= 256 (TF_ERR_UNSUPPORTED otherwise).  Waits for completion.  Stands in for the per-tile
+ * cblas_sgemm of the reference (fusion/gcn/GCN_Layer_MKL_Forward_Utils.h:233). */
+int tf_gemm_tc_dev(const float *B, const float *W, int w_transposed, int m, int K, int N, float *T, void *stream);
+
 /* SpMM-SpMM, D = A * (A * C), for callers that cannot allocate device memory.
  *
  * Has no counterpart in the reference.  It is meant for host code that is not allowed to call

@@ -43,7 +43,7 @@ EXPORTS = [
     "tf_plan_info", "tf_plan_status", "tf_exec_spmm_spmm", "tf_exec_gemm_spmm", "tf_exec_sddmm_spmm",
     "tf_exec_phase", "tf_plan_intermediate", "tf_plan_exchange_buffers", "tf_spmm_spmm_host", "tf_gemm_spmm_host",
     "tf_sddmm_spmm_host", "tf_spmm_dev", "tf_fill_uniform", "tf_fill_normal", "tf_plan_preview", "tf_free", "tf_plan_set_wait_limit", "tf_tiling_preview", "tf_plan_tile_info", "tf_spmm_spmm_noalloc",
-    "tf_noalloc_max_floats",
+    "tf_noalloc_max_floats", "tf_gemm_tc_dev",
 ]
 
 _lib = None
@@ -99,6 +99,7 @@ def lib() -> C.CDLL:
     L.tf_plan_tile_info.argtypes = [vp, ip]
     L.tf_spmm_spmm_noalloc.argtypes = [vp, vp, vp, i, vp, i, vp, vp]
     L.tf_noalloc_max_floats.restype = C.c_longlong
+    L.tf_gemm_tc_dev.argtypes = [vp, vp, i, i, i, i, vp, vp]
     L.tf_free.restype = None
     _lib = L
     return L
