@@ -1,11 +1,14 @@
 // C ABI of libtilefusion_b200: plans (device-resident operators + item lists) and executors.
 #include <cuda_runtime.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <string>
 #include <vector>
 
+#include "gemm_tc_host.h"
 #include "kernels.cuh"
 #include "launch.h"
 #include "tf_internal.h"
@@ -93,6 +96,10 @@ struct tf_plan {
   } ptile, ctile;
   size_t dyn_smem = 0;
   int tile_slots = 0;
+  // tensor-core dense producer
+  bool use_tc = false;
+  DevBuf<float> w_hi, w_lo;  // split, transposed weight [n_cols][k]
+  CUtensorMap tm_whi, tm_wlo;
   int tile_info[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // producer bx,by,bz,tiles ; consumer bx,by,bz,tiles
   // schedule mode
   DevBuf<int> s_ptr2, s_id, s_type, s_ker;
@@ -142,6 +149,13 @@ int finish_plan(tf_plan &p, const tf_plan_opts &o, int sm_count, bool ring) {
   if (p.dyn_smem > 0) { p.vec = 4; p.ch = 1; }
   int occ = tfk::stream_occupancy(p.chain, p.vec, p.ch, ring, p.dyn_smem);
   if (occ <= 0) return fail(TF_ERR_CUDA, "occupancy query failed for the executor kernel");
+  if (getenv("TF_DEBUG"))
+    fprintf(stderr, "[tf] chain %d vec %d ch %d ring %d dyn_smem %zu -> %d CTAs/SM\n", p.chain, p.vec, p.ch, (int)ring,
+            p.dyn_smem, occ);
+  // The resident-CTA query answers 1 for any kernel that allocates tensor memory.  Two CTAs of this
+  // kernel fit an SM (256 of 512 tensor-memory columns each, half the shared memory, 64 registers), and
+  // the executor does not depend on the answer for progress: only running CTAs hold tickets.
+  if (p.use_tc && occ == 1 && p.dyn_smem <= 106 * 1024) occ = 2;
   if (o.ctas_per_sm > 0) occ = std::min(occ, o.ctas_per_sm);
   p.grid = sm_count * occ;
   return TF_OK;
@@ -273,6 +287,21 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
       pp.max_ctas = p->grid;
     }
   }
+  // dense producer on the tensor cores: 128-row tiles, its K slices live in the same dynamic buffer
+  const bool want_tc = chain == 1 && o.mode != TF_MODE_SCHEDULE && o.tensor_cores >= 0 && tfk::tc_supported(k_dim, n_cols);
+  if (want_tc) {
+    p->use_tc = true;
+    p->dyn_smem = std::max(p->dyn_smem, (size_t)tfk::tc_smem_bytes_host(n_cols));
+    if (o.rows_per_block == 0) pp.rows_per_block = tfk::kTcRowsHost;
+    pp.max_block_nnz = pp.rows_per_block * 32;
+    rc = p->w_hi.alloc((size_t)k_dim * n_cols);
+    if (rc == TF_OK) rc = p->w_lo.alloc((size_t)k_dim * n_cols);
+    if (rc == TF_OK) rc = tfk::tc_make_map(&p->tm_whi, p->w_hi.p, n_cols, k_dim, n_cols);
+    if (rc == TF_OK) rc = tfk::tc_make_map(&p->tm_wlo, p->w_lo.p, n_cols, k_dim, n_cols);
+    if (rc == TF_OK) rc = finish_plan(*p, o, sm_count, false);
+    if (rc != TF_OK) return rc;
+    pp.max_ctas = p->grid;
+  }
   p->tile_info[0] = pt.bx; p->tile_info[1] = pt.by; p->tile_info[2] = pt.bz; p->tile_info[3] = pt.tiles();
   p->tile_info[4] = ct.bx; p->tile_info[5] = ct.by; p->tile_info[6] = ct.bz; p->tile_info[7] = ct.tiles();
   rc = tf::build_stream_plan(pp, F ? F->ap : nullptr, F ? F->ai : nullptr, A->ap, A->ai, &pt, &ct, p->hp);
@@ -353,12 +382,27 @@ int check_tiled_alignment(const tf_plan &p, const tfk::Params &P) {
   return TF_OK;
 }
 
+// Tensor-core producer: split the weight for this call and describe B to the TMA unit.
+int prepare_tc(tf_plan &p, tfk::Params &P, cudaStream_t s) {
+  P.use_tc = 0;
+  if (!p.use_tc) return TF_OK;
+  TF_CUDA(tfk::tc_split_weight(P.in1, P.w_transposed, p.k_dim, p.n_cols, p.w_hi.p, p.w_lo.p, s));
+  int rc = tfk::tc_make_map(&P.tm_a, P.in0, p.m, p.k_dim, tfk::kTcRowsHost);
+  if (rc != TF_OK) return rc;
+  P.tm_whi = p.tm_whi;
+  P.tm_wlo = p.tm_wlo;
+  P.use_tc = 1;
+  return TF_OK;
+}
+
 int run_phases(tf_plan &p, tfk::Params &P, int first_phase, int last_phase, cudaStream_t s) {
   int vec, ch;
   call_shape(p, {P.in0, P.in1, P.in2, P.out}, &vec, &ch);
   int rca = check_tiled_alignment(p, P);
   if (rca != TF_OK) return rca;
   if (p.dyn_smem > 0) { vec = 4; ch = 1; }  // the tiled kernel variant; its direct items loop over panels
+  rca = prepare_tc(p, P, s);
+  if (rca != TF_OK) return rca;
   const bool ring = p.hp.ring_rows > 0;
   if (first_phase <= 1 && last_phase >= 1) ++p.epoch;  // a new pass over the producer blocks
   P.epoch = p.epoch;
@@ -383,6 +427,8 @@ int run_unfused(tf_plan &p, tfk::Params &P, cudaStream_t s) {
   int rca = check_tiled_alignment(p, P);
   if (rca != TF_OK) return rca;
   if (p.dyn_smem > 0) { vec = 4; ch = 1; }
+  rca = prepare_tc(p, P, s);
+  if (rca != TF_OK) return rca;
   ++p.epoch;
   P.epoch = p.epoch;
   const int np = P.n_prod;

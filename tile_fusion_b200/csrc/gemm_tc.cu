@@ -8,6 +8,8 @@
 
 namespace tfk {
 
+static_assert(kTcRowsHost == kTcRows, "host and device tile heights differ");
+
 // Wt_hi / Wt_lo [N][K] (K contiguous) from W [K][N], or from W [N][K] when w_transposed.
 __global__ void split_weight_kernel(const float *__restrict__ W, int w_transposed, int K, int N,
                                     float *__restrict__ hi, float *__restrict__ lo) {

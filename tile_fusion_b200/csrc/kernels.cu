@@ -1,7 +1,9 @@
 // Kernels and launchers of the fused sparse-dense chains (sm_100a).  See kernels.cuh.
 #include <cstdio>
+#include <cstdlib>
 
 #include "kernels.cuh"
+#include "gemm_tc.cuh"
 #include "launch.h"
 
 namespace tfk {
@@ -162,9 +164,10 @@ union StreamSmem {
 // SM, so that variant may use twice the registers.
 template <int MODE, int VEC, int CH, bool RING, bool TILED>
 __global__ void __launch_bounds__(TILED ? kTiledThreads : kThreads, TILED ? 2 : TF_MIN_CTAS)
-    stream_kernel(const Params P) {
+    stream_kernel(const __grid_constant__ Params P) {
   constexpr int NT = TILED ? kTiledThreads : kThreads;
   constexpr int NW = NT / 32;
+  constexpr bool HAS_TC = MODE == 1 && TILED;  // the dense producer may run on the tensor cores
   __shared__ StreamSmem sm;
   __shared__ int s_next;
   __shared__ int s_ok;
@@ -173,6 +176,11 @@ __global__ void __launch_bounds__(TILED ? kTiledThreads : kThreads, TILED ? 2 : 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   ExecState *st = P.st;
   const int n_items = P.item_end - P.item_begin;
+  __shared__ TcShared tc;
+  unsigned tc_phase = 0;
+  char *smem1024 = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(stage) + 1023) & ~(uintptr_t)1023);
+  const bool use_tc = HAS_TC && P.use_tc != 0;
+  if (use_tc) tc_begin(tc);
 
   if (threadIdx.x == 0) s_next = atomicAdd(&st->ticket, 1);
   __syncthreads();
@@ -211,7 +219,15 @@ __global__ void __launch_bounds__(TILED ? kTiledThreads : kThreads, TILED ? 2 : 
         return dst_base + (size_t)t * P.n_cols;
       };
       if (MODE == 1) {
-        gemm_rows_cta(P.in0, P.in1, P.w_transposed != 0, rb, re, P.k_dim, P.n_cols, dst_row, sm.g);
+        if (HAS_TC && use_tc) {
+          if (!tc_gemm_rows<NT>(&P.tm_a, &P.tm_whi, &P.tm_wlo, rb, re, P.k_dim, P.n_cols, dst_row, smem1024, tc,
+                                tc_phase, P.spin_limit)) {
+            if (threadIdx.x == 0) atomicExch(&st->error, 1);
+            break;
+          }
+        } else {
+          gemm_rows_cta(P.in0, P.in1, P.w_transposed != 0, rb, re, P.k_dim, P.n_cols, dst_row, sm.g);
+        }
       } else {
         if (re - rb == 1 && __ldg(P.f_ap + re) - __ldg(P.f_ap + rb) >= kHeavyNnz)
           spmm_row_cta<NT, VEC, CH, false, false>(P.f_ap, P.f_ai, P.f_ax, rb, P.in0, P.n_cols, dst_row(rb), false,
@@ -273,6 +289,7 @@ __global__ void __launch_bounds__(TILED ? kTiledThreads : kThreads, TILED ? 2 : 
     __syncthreads();
     cur = s_next;
   }
+  if (use_tc) tc_end(tc);
   // the last CTA out rewinds the ticket counter (and, after the last phase, the watermarks)
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -371,7 +388,7 @@ __global__ void fill_normal_kernel(float *p, long long n, unsigned long long see
 // ---------------------------------------------------------------------------
 // Launchers
 // ---------------------------------------------------------------------------
-typedef void (*StreamFn)(const Params);
+typedef void (*StreamFn)(const __grid_constant__ Params);
 typedef void (*SchedFn)(const Params, const SchedParams);
 
 template <int MODE, int VEC, int CH>
@@ -413,6 +430,12 @@ int stream_occupancy(int mode, int vec, int ch, bool ring, size_t dyn_smem) {
       cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem) != cudaSuccess)
     return -1;
   cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, dyn_smem > 0 ? kTiledThreads : kThreads, dyn_smem);
+  if (getenv("TF_DEBUG")) {
+    cudaFuncAttributes a;
+    if (cudaFuncGetAttributes(&a, fn) == cudaSuccess)
+      fprintf(stderr, "[tf] kernel regs %d static smem %zu local %zu maxThreads %d maxDyn %d -> %d\n", a.numRegs,
+              a.sharedSizeBytes, a.localSizeBytes, a.maxThreadsPerBlock, a.maxDynamicSharedSizeBytes, nb);
+  }
   return e == cudaSuccess ? nb : -1;
 }
 

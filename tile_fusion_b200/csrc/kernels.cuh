@@ -8,6 +8,7 @@
 // contiguous watermark; consumers wait (bounded) on the watermark.  T is read
 // with L2-only loads because other SMs write it during the same launch.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -56,6 +57,9 @@ struct Params {
   int relu, w_transposed;
   int reset_wm;      // last CTA clears the watermarks (last phase of a call)
   int spin_limit;    // polls before a wait gives up
+  // tensor-core dense producer (GeMM-SpMM): TMA descriptors of B and of the split, transposed weight
+  alignas(64) CUtensorMap tm_a, tm_whi, tm_wlo;
+  int use_tc;
   TileArrays pt, ct; // gather tiles of the first / second operator (null when not tiled)
   int tile_slots;    // staging slots per CTA (dynamic shared memory holds tile_slots * 132 bytes)
 };
