@@ -50,7 +50,7 @@ def measured_peak_gbs():
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU while the timed region runs (read-only NVML)."""
 
-    def __init__(self, index: int, period=0.05):
+    def __init__(self, index: int, period=0.005):
         self.index, self.period = index, period
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()

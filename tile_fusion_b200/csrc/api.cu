@@ -312,6 +312,9 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
   rc = finish_plan(*p, o, sm_count, p->hp.ring_rows > 0);
   if (rc != TF_OK) return rc;
 
+  // with a halo exchange in flight, leave a few SMs half empty so that the NCCL send/recv kernels can
+  // start while the persistent executor occupies the GPU (they would otherwise wait for it to drain)
+  if ((o.halo_rows > 0 || o.n_boundary > 0) && p->grid > sm_count) p->grid = std::max(sm_count, p->grid - 16);
   // phase 0 items: boundary rows -> send buffer, in runs of consecutive rows
   if (!pp.boundary_rows.empty()) {
     std::vector<tf::Item> pre;

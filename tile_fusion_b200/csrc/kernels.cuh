@@ -360,7 +360,6 @@ __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, cons
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < kTileRowsPerGroup; ++j) {
-      if (j * kTileGroups >= nR) break;  // uniform over the CTA
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {

@@ -32,10 +32,17 @@ Lattice detect_lattice(int m, const int *ap, const int *ai) {
     for (int j = ap[r]; j < ap[r + 1]; ++j) ++hist[ai[j] - r];
     if (hist.size() > 4096) return L;  // unstructured
   }
-  std::vector<int> pos;
+  // frequent offsets; the middle one is the operator's own diagonal (0 for a square operator, a
+  // constant shift when the columns were renumbered, as for one rank's rows of a partitioned chain)
+  std::vector<int> freq;
   for (auto &kv : hist)
-    if (kv.first > 0 && kv.second * 2 >= sampled) pos.push_back(kv.first);
-  std::sort(pos.begin(), pos.end());
+    if (kv.second * 2 >= sampled) freq.push_back(kv.first);
+  std::sort(freq.begin(), freq.end());
+  if (freq.empty() || freq.size() % 2 == 0) return L;
+  const int d0 = freq[freq.size() / 2];
+  std::vector<int> pos;
+  for (int f : freq)
+    if (f > d0) pos.push_back(f - d0);
   if (pos.empty() || pos[0] != 1 || pos.size() > 3) return L;
   L.dims = (int)pos.size();
   if (L.dims >= 2) L.nx = pos[1];
@@ -114,6 +121,9 @@ int build_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_bz, 
       return;
     }
     if ((int)(out.halo.size() - h0) > slot_cap) { out.tiled = false; out.failed = true; return; }
+    // slots in source-row order: consecutive rows of a band then read consecutive slots
+    std::sort(out.halo.begin() + h0, out.halo.end());
+    for (size_t q = h0; q < out.halo.size(); ++q) where[out.halo[q]] = (int)(q - h0);
     for (int i = 0; i < n; ++i) {
       out.rows.push_back(rs[i]);
       for (int j = ap[rs[i]]; j < ap[rs[i] + 1]; ++j) out.slot[j] = (uint16_t)where[ai[j]];

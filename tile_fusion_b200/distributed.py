@@ -52,22 +52,28 @@ class RankChain:
         self.sendbuf = _as_tensor(sp, sr, n_cols, self.device)
         self.halobuf = _as_tensor(hp, hr, n_cols, self.device)
         self.comm_stream = torch.cuda.Stream(device=self.device)
+        self._ready, self._arrived = torch.cuda.Event(), torch.cuda.Event()
+        self._ops = None
         self._gather_idx = {s.peer: torch.as_tensor(s.index, device=self.device) for s in lay.send
                             if s.index is not None}
 
     def exchange_ops(self, dist):
-        """P2P ops of one halo exchange (send buffer segments out, halo segments in)."""
-        ops, keep = [], []
+        """P2P ops of one halo exchange (send buffer segments out, halo segments in).  The op objects
+        name fixed device buffers, so they are built once and reused by every step."""
+        if self._ops is not None:
+            return self._ops
+        ops, gathers = [], []
         for s in self.lay.send:
             if s.index is None:
                 t = self.sendbuf[s.start:s.start + s.count]
-            else:
-                t = self.sendbuf.index_select(0, self._gather_idx[s.peer])
-                keep.append(t)
+            else:  # non-contiguous rows: gathered into a staging tensor before each send
+                t = self.sendbuf.new_empty((s.count, self.n_cols))
+                gathers.append((t, self._gather_idx[s.peer]))
             ops.append(dist.P2POp(dist.isend, t, s.peer))
         for s in self.lay.recv:
             ops.append(dist.P2POp(dist.irecv, self.halobuf[s.start:s.start + s.count], s.peer))
-        return ops, keep
+        self._ops = (ops, gathers)
+        return self._ops
 
     def step(self, in0, in1, out, dist=None, w_transposed=False, relu=False, exchange=None):
         """One pass.  `dist` = torch.distributed (NCCL) or None with `exchange(self)` a callable that
@@ -78,17 +84,17 @@ class RankChain:
         if len(self.lay.boundary_rows):
             self.plan.phase(0, in0, in1, None, w_transposed, relu)
         if has_x and dist is not None:
-            ready = torch.cuda.Event()
-            ready.record(main)
+            self._ready.record(main)
             with torch.cuda.stream(self.comm_stream):
-                self.comm_stream.wait_event(ready)
-                ops, keep = self.exchange_ops(dist)
+                self.comm_stream.wait_event(self._ready)
+                ops, gathers = self.exchange_ops(dist)
+                for t, idx in gathers:
+                    torch.index_select(self.sendbuf, 0, idx, out=t)
                 for r in dist.batch_isend_irecv(ops):
                     r.wait()
-                arrived = torch.cuda.Event()
-                arrived.record(self.comm_stream)
+                self._arrived.record(self.comm_stream)
             self.plan.phase(1, in0, in1, out, w_transposed, relu)
-            main.wait_event(arrived)
+            main.wait_event(self._arrived)
         else:
             self.plan.phase(1, in0, in1, out, w_transposed, relu)
             if exchange is not None:
