@@ -106,7 +106,18 @@ struct tf_plan {
   int s_n1 = 0;
   std::vector<int> s_ptr1;
   bool s_has_ker = false;
-  // host-pointer path staging
+  // host-pointer path: staging buffers, streams and the segments of the copy/compute pipeline
+  struct Seg { int item_begin, item_end; long long in_rows, out_rows; };
+  std::vector<Seg> segs;
+  cudaStream_t s_h2d = nullptr, s_run = nullptr, s_d2h = nullptr;
+  std::vector<cudaEvent_t> ev_in, ev_run;
+  ~tf_plan() {
+    for (cudaEvent_t e : ev_in) cudaEventDestroy(e);
+    for (cudaEvent_t e : ev_run) cudaEventDestroy(e);
+    if (s_h2d) cudaStreamDestroy(s_h2d);
+    if (s_run) cudaStreamDestroy(s_run);
+    if (s_d2h) cudaStreamDestroy(s_d2h);
+  }
   DevBuf<float> h_in0, h_in1, h_in2, h_out;
   int grid = 0, vec = 1, ch = 1;
   int epoch = 1;  // flags start at 0, so no pass may use 0
@@ -212,6 +223,8 @@ int load_schedule(tf_plan &p, const tf_schedule *s, bool need_ker) {
   return rc;
 }
 
+void build_segments(tf_plan &p, int n_seg);
+
 // Common plan construction for the two-operator chains.
 int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int n_cols, const tf_plan_opts *opts,
                     const tf_schedule *sched, tf_plan **out) {
@@ -274,11 +287,13 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
   pp.slack_blocks = o.mode == TF_MODE_UNFUSED ? (1 << 30) : o.slack_blocks;
   // gather tiles: 16-byte staging copies need rows that are multiples of 4 floats
   tf::Tiling pt, ct;
-  const int slots = o.tile_slots == 0 ? tf::kDefaultTileSlots : o.tile_slots;
+  // a tile holds one row per 4 lanes... of the CTA that runs it: 256 rows (sparse chains) or 512 (GeMM-SpMM)
+  const int tile_rows = tfk::tiled_threads(chain);
+  const int slots = o.tile_slots == 0 ? (chain == 1 ? tf::kDefaultTileSlots : tf::kDefaultTileSlotsSmall) : o.tile_slots;
   if (o.mode != TF_MODE_SCHEDULE && slots > 0 && n_cols % 4 == 0) {
     const int max_bz = o.tile_max_bz > 0 ? o.tile_max_bz : tf::kDefaultTileMaxBz;
-    if (F) tf::build_tiling(F->m, F->ap, F->ai, slots, max_bz, pt);
-    tf::build_tiling(A->m, A->ap, A->ai, slots, max_bz, ct);
+    if (F) tf::build_tiling(F->m, F->ap, F->ai, slots, max_bz, tile_rows, pt);
+    tf::build_tiling(A->m, A->ap, A->ai, slots, max_bz, tile_rows, ct);
     if (pt.tiled || ct.tiled) {
       p->dyn_smem = (size_t)slots * 132;  // 128 B of staging + one source row id per slot
       p->tile_slots = slots;
@@ -336,6 +351,7 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
     rc = p->sendbuf.alloc(pp.boundary_rows.size() * (size_t)n_cols);
     if (rc != TF_OK) return rc;
   }
+  if (o.mode == TF_MODE_STREAM && !o.halo_rows && !o.n_boundary) build_segments(*p, 16);
   rc = upload_items(*p);
   if (rc == TF_OK) rc = zero_state(*p);
   if (rc == TF_OK) rc = p->inter.alloc((size_t)p->hp.inter_rows * n_cols);
@@ -366,6 +382,7 @@ tfk::Params base_params(tf_plan &p) {
   P.pt = p.ptile.view();
   P.ct = p.ctile.view();
   P.tile_slots = p.tile_slots;
+  if (const char *f = getenv("TF_DEBUG_FLAGS")) P.debug_flags = atoi(f);
   P.spin_limit = p.spin_limit;
   return P;
 }
@@ -420,6 +437,86 @@ int run_phases(tf_plan &p, tfk::Params &P, int first_phase, int last_phase, cuda
     TF_CUDA(tfk::launch_stream(p.chain, vec, ch, ring, p.grid, p.dyn_smem, Q, s));
     ++p.launches;
   }
+  return TF_OK;
+}
+
+// Segments of the item list for the host pipeline: after segment j, the producers listed so far have
+// read input rows < in_rows, and every output row < out_rows is final.
+void build_segments(tf_plan &p, int n_seg) {
+  p.segs.clear();
+  const int b = p.hp.phase_begin[1], e = p.hp.phase_begin[2];
+  const int n = e - b;
+  if (n <= 0 || p.hp.phase_begin[3] != e) return;
+  n_seg = std::max(1, std::min(n_seg, n / std::max(1, p.grid)));
+  std::vector<int> suffix_min(n + 1, p.m);
+  for (int i = n - 1; i >= 0; --i) {
+    const tf::Item &it = p.hp.items[b + i];
+    const bool cons = it.kind == tf::ITEM_CONSUME || it.kind == tf::ITEM_CONSUME_TILED;
+    suffix_min[i] = std::min(suffix_min[i + 1], cons ? it.aux1 : p.m);
+  }
+  long long in_rows = 0;
+  for (int s = 0; s < n_seg; ++s) {
+    const int i0 = (int)((long long)n * s / n_seg), i1 = (int)((long long)n * (s + 1) / n_seg);
+    for (int i = i0; i < i1; ++i) {
+      const tf::Item &it = p.hp.items[b + i];
+      if (it.kind == tf::ITEM_PRODUCE || it.kind == tf::ITEM_PRODUCE_TILED) in_rows = std::max<long long>(in_rows, it.aux0 + 1LL);
+    }
+    p.segs.push_back(tf_plan::Seg{b + i0, b + i1, in_rows, (long long)suffix_min[i1]});
+  }
+}
+
+// Host pipeline: the dense input is copied in row chunks on one stream, the item list runs in segments
+// on a second as soon as the rows a segment reads have arrived, and finished output rows leave on a
+// third.  in_rows x in_cols floats come from h_in; D is m x n_cols.
+int run_host_pipeline(tf_plan &p, tfk::Params &P, const float *h_in, long long in_rows, int in_cols, float *d_in,
+                      float *h_out, float *d_out) {
+  if (!p.s_h2d) {
+    TF_CUDA(cudaStreamCreateWithFlags(&p.s_h2d, cudaStreamNonBlocking));
+    TF_CUDA(cudaStreamCreateWithFlags(&p.s_run, cudaStreamNonBlocking));
+    TF_CUDA(cudaStreamCreateWithFlags(&p.s_d2h, cudaStreamNonBlocking));
+  }
+  const int ns = (int)p.segs.size();
+  while ((int)p.ev_in.size() < ns) {
+    cudaEvent_t a, b;
+    TF_CUDA(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+    TF_CUDA(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+    p.ev_in.push_back(a); p.ev_run.push_back(b);
+  }
+  int vec, ch;
+  call_shape(p, {P.in0, P.in1, P.in2, P.out}, &vec, &ch);
+  if (p.dyn_smem > 0) { vec = 4; ch = 1; }
+  int rc = prepare_tc(p, P, p.s_run);
+  if (rc != TF_OK) return rc;
+  const bool ring = p.hp.ring_rows > 0;
+  ++p.epoch;
+  P.epoch = p.epoch;
+  p.launches = 0;
+  long long in_done = 0, out_done = 0;
+  for (int s = 0; s < ns; ++s) {
+    const tf_plan::Seg &g = p.segs[s];
+    const long long in_to = s == ns - 1 ? in_rows : std::min(in_rows, g.in_rows);
+    if (in_to > in_done)
+      TF_CUDA(cudaMemcpyAsync(d_in + in_done * in_cols, h_in + in_done * in_cols, (size_t)(in_to - in_done) * in_cols * 4,
+                              cudaMemcpyHostToDevice, p.s_h2d));
+    in_done = std::max(in_done, in_to);
+    TF_CUDA(cudaEventRecord(p.ev_in[s], p.s_h2d));
+    TF_CUDA(cudaStreamWaitEvent(p.s_run, p.ev_in[s], 0));
+    tfk::Params Q = P;
+    Q.item_begin = g.item_begin; Q.item_end = g.item_end;
+    Q.reset_wm = s == ns - 1;
+    TF_CUDA(tfk::launch_stream(p.chain, vec, ch, ring, p.grid, p.dyn_smem, Q, p.s_run));
+    ++p.launches;
+    TF_CUDA(cudaEventRecord(p.ev_run[s], p.s_run));
+    const long long out_to = s == ns - 1 ? p.m : g.out_rows;
+    if (out_to > out_done) {
+      TF_CUDA(cudaStreamWaitEvent(p.s_d2h, p.ev_run[s], 0));
+      TF_CUDA(cudaMemcpyAsync(h_out + out_done * p.n_cols, d_out + out_done * p.n_cols,
+                              (size_t)(out_to - out_done) * p.n_cols * 4, cudaMemcpyDeviceToHost, p.s_d2h));
+      out_done = out_to;
+    }
+  }
+  TF_CUDA(cudaStreamSynchronize(p.s_d2h));
+  TF_CUDA(cudaStreamSynchronize(p.s_run));
   return TF_OK;
 }
 
@@ -528,7 +625,7 @@ int tf_plan_info(const tf_plan *p, long long info[8]) {
   info[2] = p->hp.n_cons;
   info[3] = p->hp.ring_rows;
   info[4] = p->grid;
-  info[5] = p->dyn_smem > 0 ? tfk::kTiledThreads : tfk::kThreads;
+  info[5] = p->dyn_smem > 0 ? tfk::tiled_threads(p->chain) : tfk::kThreads;
   info[6] = p->launches;
   info[7] = p->hp.inter_rows;
   return TF_OK;
@@ -644,6 +741,17 @@ int tf_spmm_spmm_host(tf_plan *p, const float *C, float *D) {
   int rc = set_device(*p);
   if (rc != TF_OK) return rc;
   const size_t nd = (size_t)p->m * p->n_cols;
+  if (p->segs.size() > 1) {
+    const size_t nin = (size_t)p->first_cols * p->n_cols;
+    if (p->h_in0.n < nin) rc = p->h_in0.alloc(nin);
+    if (rc == TF_OK && p->h_out.n < nd) rc = p->h_out.alloc(nd);
+    if (rc != TF_OK) return rc;
+    tfk::Params P = base_params(*p);
+    P.in0 = p->h_in0.p; P.out = p->h_out.p;
+    rc = run_host_pipeline(*p, P, C, p->first_cols, p->n_cols, p->h_in0.p, D, p->h_out.p);
+    if (rc != TF_OK) return rc;
+    return tf_plan_status(p, nullptr);
+  }
   rc = stage_in(p->h_in0, C, (size_t)p->first_cols * p->n_cols, 0);
   if (rc == TF_OK && p->h_out.n < nd) rc = p->h_out.alloc(nd);
   if (rc == TF_OK) rc = tf_exec_spmm_spmm(p, p->h_in0.p, p->h_out.p, nullptr);
@@ -657,6 +765,24 @@ int tf_gemm_spmm_host(tf_plan *p, const float *B, const float *W, int w_transpos
   int rc = set_device(*p);
   if (rc != TF_OK) return rc;
   const size_t nd = (size_t)p->m * p->n_cols;
+  if (p->segs.size() > 1) {
+    const size_t nin = (size_t)p->m * p->k_dim;
+    if (p->h_in0.n < nin) rc = p->h_in0.alloc(nin);
+    if (rc == TF_OK && p->h_out.n < nd) rc = p->h_out.alloc(nd);
+    if (rc != TF_OK) return rc;
+    if (!p->s_run) {
+      TF_CUDA(cudaStreamCreateWithFlags(&p->s_h2d, cudaStreamNonBlocking));
+      TF_CUDA(cudaStreamCreateWithFlags(&p->s_run, cudaStreamNonBlocking));
+      TF_CUDA(cudaStreamCreateWithFlags(&p->s_d2h, cudaStreamNonBlocking));
+    }
+    rc = stage_in(p->h_in1, W, (size_t)p->k_dim * p->n_cols, p->s_run);  // the weight first, on the stream that uses it
+    if (rc != TF_OK) return rc;
+    tfk::Params P = base_params(*p);
+    P.in0 = p->h_in0.p; P.in1 = p->h_in1.p; P.out = p->h_out.p; P.w_transposed = w_transposed; P.relu = relu;
+    rc = run_host_pipeline(*p, P, B, p->m, p->k_dim, p->h_in0.p, D, p->h_out.p);
+    if (rc != TF_OK) return rc;
+    return tf_plan_status(p, nullptr);
+  }
   rc = stage_in(p->h_in0, B, (size_t)p->m * p->k_dim, 0);
   if (rc == TF_OK) rc = stage_in(p->h_in1, W, (size_t)p->k_dim * p->n_cols, 0);
   if (rc == TF_OK && p->h_out.n < nd) rc = p->h_out.alloc(nd);

@@ -163,9 +163,9 @@ union StreamSmem {
 // TILED: the plan holds gather tiles (item kinds 4 and 5); their staging buffer allows two CTAs per
 // SM, so that variant may use twice the registers.
 template <int MODE, int VEC, int CH, bool RING, bool TILED>
-__global__ void __launch_bounds__(TILED ? kTiledThreads : kThreads, TILED ? 2 : TF_MIN_CTAS)
+__global__ void __launch_bounds__(TILED ? tiled_threads(MODE) : kThreads, TILED ? 2 : TF_MIN_CTAS)
     stream_kernel(const __grid_constant__ Params P) {
-  constexpr int NT = TILED ? kTiledThreads : kThreads;
+  constexpr int NT = TILED ? tiled_threads(MODE) : kThreads;
   constexpr int NW = NT / 32;
   constexpr bool HAS_TC = MODE == 1 && TILED;  // the dense producer may run on the tensor cores
   __shared__ StreamSmem sm;
@@ -268,14 +268,15 @@ __global__ void __launch_bounds__(TILED ? kTiledThreads : kThreads, TILED ? 2 : 
         if (RING) { t = r - base; if (t >= ring) t -= ring; }
         return P.inter + (size_t)t * P.n_cols;
       };
-      tile_gather<false>(P.pt, rb, P.f_ap, P.f_ax, P.in0, P.n_cols, dst_row, false, 0, 0, 0, stage, hrow);
+      tile_gather<NT, false>(P.pt, rb, P.f_ap, P.f_ax, P.in0, P.n_cols, dst_row, false, 0, 0, 0, stage, hrow,
+                         P.debug_flags);
       __syncthreads();
       if (threadIdx.x == 0) publish(P.prod_done, block, P.epoch);
     } else if (TILED && kind == 5) {
       // ---- consume: the rows of one gather tile of the second operator ----
       auto out_row = [&](int r) -> float * { return P.out + (size_t)r * P.n_cols; };
-      tile_gather<RING>(P.ct, rb, P.s_ap, P.s_ax, P.inter, P.n_cols, out_row, P.relu != 0, base, P.ring_rows,
-                        P.m_local, stage, hrow);
+      tile_gather<NT, RING>(P.ct, rb, P.s_ap, P.s_ax, P.inter, P.n_cols, out_row, P.relu != 0, base, P.ring_rows,
+                        P.m_local, stage, hrow, P.debug_flags);
       if (RING) {
         __syncthreads();
         if (threadIdx.x == 0) publish(P.cons_done, block, P.epoch);
@@ -429,7 +430,7 @@ int stream_occupancy(int mode, int vec, int ch, bool ring, size_t dyn_smem) {
   if (dyn_smem > 0 &&
       cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem) != cudaSuccess)
     return -1;
-  cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, dyn_smem > 0 ? kTiledThreads : kThreads, dyn_smem);
+  cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, dyn_smem > 0 ? tiled_threads(mode) : kThreads, dyn_smem);
   if (getenv("TF_DEBUG")) {
     cudaFuncAttributes a;
     if (cudaFuncGetAttributes(&a, fn) == cudaSuccess)
@@ -446,7 +447,7 @@ cudaError_t launch_stream(int mode, int vec, int ch, bool ring, int grid, size_t
     cudaError_t e = cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem);
     if (e != cudaSuccess) return e;
   }
-  fn<<<grid, dyn_smem > 0 ? kTiledThreads : kThreads, dyn_smem, s>>>(p);
+  fn<<<grid, dyn_smem > 0 ? tiled_threads(mode) : kThreads, dyn_smem, s>>>(p);
   return cudaGetLastError();
 }
 

@@ -16,7 +16,10 @@ namespace tfk {
 
 constexpr int kThreads = 256;       // CTA size of the direct kernels
 constexpr int kWarps = kThreads / 32;
-constexpr int kTiledThreads = 512;  // CTA size of the gather-tile variant of the executor
+// CTA size of the gather-tile variant of the executor.  512 threads, two CTAs per SM: measured faster
+// than 256 threads x four CTAs on the 128^3 case (1.30 vs 1.41 ms), whose smaller tiles reuse less.
+__host__ __device__ constexpr int tiled_threads(int /*mode*/) { return 512; }
+constexpr int kTiledThreadsMax = 512;
 constexpr unsigned kFull = 0xffffffffu;
 
 struct ExecState {
@@ -60,6 +63,7 @@ struct Params {
   // tensor-core dense producer (GeMM-SpMM): TMA descriptors of B and of the split, transposed weight
   alignas(64) CUtensorMap tm_a, tm_whi, tm_wlo;
   int use_tc;
+  int debug_flags;   // diagnostics only: 1 = skip the tile compute loop, 2 = skip the tile staging copies
   TileArrays pt, ct; // gather tiles of the first / second operator (null when not tiled)
   int tile_slots;    // staging slots per CTA (dynamic shared memory holds tile_slots * 132 bytes)
 };
@@ -295,19 +299,18 @@ __device__ __forceinline__ void cp_async_wait_all() {
 // column chunk, so the inner loop touches shared memory only.  The two groups that share a
 // quarter-warp read opposite 64-byte halves of their slots in each load, which keeps the 128-bit
 // shared loads conflict-free.
-constexpr int kTileGroups = kTiledThreads / 4;                     // 128 groups of 4 lanes
-constexpr int kTileRowsPerGroup = 4;
-constexpr int kTileMaxRows = kTileRowsPerGroup * kTileGroups;      // 512
+constexpr int kTileRowsPerGroup = 4;  // a tile holds at most NT rows (NT / 4 groups of 4 lanes)
 constexpr int kTileMaxSlots = 1700;  // staging slots a tile may use (shared-memory capacity)
 
-template <bool SRC_RING, class DstRow>
+template <int NT, bool SRC_RING, class DstRow>
 __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, const int *__restrict__ ap,
                                             const float *__restrict__ ax, const float *__restrict__ src,
                                             int n_cols, DstRow dst_row, bool relu, int base, int ring_rows,
-                                            int m_local, float4 *stage, int *hrow) {
+                                            int m_local, float4 *stage, int *hrow, int debug_flags = 0) {
   const int rp = __ldg(ta.row_ptr + tile), nR = __ldg(ta.row_ptr + tile + 1) - rp;
   const int hp = __ldg(ta.halo_ptr + tile), nH = __ldg(ta.halo_ptr + tile + 1) - hp;
   const int g8 = threadIdx.x >> 3, l8 = threadIdx.x & 7;  // staging: 8 lanes per 128-byte slot
+  constexpr int kTileGroups = NT / 4;
   const int g4 = threadIdx.x >> 2, l4 = threadIdx.x & 3;  // compute: 4 lanes per row
   const int colA = ((g4 & 1) * 16) + l4 * 4, colB = (((g4 & 1) ^ 1) * 16) + l4 * 4;  // floats within the chunk
   const char *sA = reinterpret_cast<const char *>(stage) + colA * 4;
@@ -339,22 +342,22 @@ __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, cons
   // source row of every slot, resolved once per tile: all loads are in flight together
   __syncthreads();  // the previous tile's readers are done with hrow and the buffer
   {
-    int v[kTileMaxSlots / kTiledThreads + 1];
+    int v[kTileMaxSlots / NT + 1];
 #pragma unroll
-    for (int u = 0; u < kTileMaxSlots / kTiledThreads + 1; ++u) {
-      const int s = threadIdx.x + u * kTiledThreads;
+    for (int u = 0; u < kTileMaxSlots / NT + 1; ++u) {
+      const int s = threadIdx.x + u * NT;
       v[u] = s < nH ? __ldg(ta.halo + hp + s) : 0;
     }
 #pragma unroll
-    for (int u = 0; u < kTileMaxSlots / kTiledThreads + 1; ++u) {
-      const int s = threadIdx.x + u * kTiledThreads;
+    for (int u = 0; u < kTileMaxSlots / NT + 1; ++u) {
+      const int s = threadIdx.x + u * NT;
       if (s < nH) hrow[s] = map_row<SRC_RING>(v[u], base, ring_rows, m_local);
     }
   }
   for (int c0 = 0; c0 < n_cols; c0 += 32) {
     __syncthreads();  // hrow is complete; the previous chunk's readers are done with the buffer
-    if (c0 + l8 * 4 < n_cols)
-      for (int s = g8; s < nH; s += kTiledThreads / 8)
+    if (c0 + l8 * 4 < n_cols && !(debug_flags & 2))
+      for (int s = g8; s < nH; s += NT / 8)
         cp_async16(stage + s * 8 + l8, src + (size_t)hrow[s] * n_cols + c0 + l8 * 4);
     cp_async_wait_all();
     __syncthreads();
@@ -363,7 +366,7 @@ __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, cons
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        if (k < kshort) {  // uniform over the warp
+        if (k < kshort && !(debug_flags & 1)) {  // uniform over the warp
           const int off = __shfl_sync(kFull, ms[j][k >> 2], k & 3, 4);
           const float v = __shfl_sync(kFull, mv[j][k >> 2], k & 3, 4);
           const float4 x = *reinterpret_cast<const float4 *>(sA + off);

@@ -45,7 +45,7 @@ inline int block_of(const std::vector<int> &bounds, int row) {
 
 }  // namespace
 
-int build_stream_plan(const PlanParams &pp, const int *first_ap, const int * /*first_ai*/, const int *sec_ap,
+int build_stream_plan(const PlanParams &pp, const int *first_ap, const int *first_ai, const int *sec_ap,
                       const int *sec_ai, const Tiling *ptile, const Tiling *ctile, HostPlan &out) {
   const int m = pp.m;
   const int rb = pp.rows_per_block;
@@ -92,6 +92,22 @@ int build_stream_plan(const PlanParams &pp, const int *first_ap, const int * /*f
   }
 
   // every resident CTA holds the item it works on and the next ticket, about half of them producers
+  // bounds used by the host pipeline that overlaps copies with execution
+  std::vector<int> psrc_max(np, 0), cout_min(nc, 0);
+  for (int j = 0; j < np; ++j) {
+    int mx = 0;
+    if (pp.producer_is_gemm) mx = pmax[j];
+    else if (p_tiled) { for (int k = ptile->tile_halo_ptr[j]; k < ptile->tile_halo_ptr[j + 1]; ++k) mx = std::max(mx, ptile->halo[k]); }
+    else { for (int r = out.prod_rows[j]; r < out.prod_rows[j + 1]; ++r) for (int q = first_ap[r]; q < first_ap[r + 1]; ++q) mx = std::max(mx, first_ai[q]); }
+    psrc_max[j] = mx;
+  }
+  for (int c = 0; c < nc; ++c) {
+    int mn = INT_MAX;
+    if (c_tiled) { for (int k = ctile->tile_row_ptr[c]; k < ctile->tile_row_ptr[c + 1]; ++k) mn = std::min(mn, ctile->rows[k]); }
+    else mn = out.cons_rows[c];
+    cout_min[c] = mn == INT_MAX ? 0 : mn;
+  }
+
   int slack = pp.slack_blocks >= 0 ? pp.slack_blocks : std::max(1, pp.max_ctas + 8);
   slack = std::min(slack, np);
   const bool multi = pp.halo_rows > 0 || !pp.boundary_rows.empty();
@@ -148,6 +164,7 @@ int build_stream_plan(const PlanParams &pp, const int *first_ap, const int * /*f
     it.row_end = c_tiled ? c + 1 : out.cons_rows[c + 1];
     it.need = need[c];
     it.base = (ring_rows && cmin[c] != INT_MAX) ? (int)((cmin[c] / ring_rows) * ring_rows) : 0;
+    it.aux1 = cout_min[c];  // lowest output row this unit writes
     out.items.push_back(it);
   };
   for (const Entry &e : order) {
@@ -159,6 +176,7 @@ int build_stream_plan(const PlanParams &pp, const int *first_ap, const int * /*f
     it.row_begin = p_tiled ? j : out.prod_rows[j];
     it.row_end = p_tiled ? j + 1 : out.prod_rows[j + 1];
     it.base = ring_rows ? (int)((pmin[j] / ring_rows) * ring_rows) : 0;
+    it.aux0 = psrc_max[j];  // highest row of the producer's dense input this unit reads
     if (ring_rows) {
       // consumers that still read the rows this unit overwrites: those with sufmin <= pmax - ring
       const long long x = (long long)pmax[j] - ring_rows;
@@ -217,10 +235,11 @@ extern "C" int tf_plan_preview(const tf_csr *A, const tf_csr *B, int producer_is
   const tf_csr *F = producer_is_gemm ? nullptr : (B ? B : A);
   tf::HostPlan hp;
   tf::Tiling pt, ct;
-  const int cap = (!o || o->tile_slots == 0) ? tf::kDefaultTileSlots : o->tile_slots;
+  const int cap = (!o || o->tile_slots == 0) ? (producer_is_gemm ? tf::kDefaultTileSlots : tf::kDefaultTileSlotsSmall) : o->tile_slots;
+  const int tile_rows = 512;
   if (cap > 0 && n_cols % 4 == 0 && !(o && o->mode == TF_MODE_SCHEDULE)) {
-    if (F) tf::build_tiling(F->m, F->ap, F->ai, cap, (o && o->tile_max_bz > 0) ? o->tile_max_bz : tf::kDefaultTileMaxBz, pt);
-    tf::build_tiling(A->m, A->ap, A->ai, cap, (o && o->tile_max_bz > 0) ? o->tile_max_bz : tf::kDefaultTileMaxBz, ct);
+    if (F) tf::build_tiling(F->m, F->ap, F->ai, cap, (o && o->tile_max_bz > 0) ? o->tile_max_bz : tf::kDefaultTileMaxBz, tile_rows, pt);
+    tf::build_tiling(A->m, A->ap, A->ai, cap, (o && o->tile_max_bz > 0) ? o->tile_max_bz : tf::kDefaultTileMaxBz, tile_rows, ct);
   }
   int rc = tf::build_stream_plan(pp, F ? F->ap : nullptr, F ? F->ai : nullptr, A->ap, A->ai, &pt, &ct, hp);
   if (rc != TF_OK) return rc;
@@ -251,8 +270,8 @@ extern "C" int tf_tiling_preview(const tf_csr *A, int tile_slots, int tile_max_b
   if (!A || !row_ptr || !rows || !halo_ptr || !halo || !n_tiles || !info)
     return tf::fail(TF_ERR_ARG, "tf_tiling_preview: null argument");
   tf::Tiling t;
-  const int cap = tile_slots == 0 ? tf::kDefaultTileSlots : tile_slots;
-  if (cap > 0) tf::build_tiling(A->m, A->ap, A->ai, cap, tile_max_bz > 0 ? tile_max_bz : tf::kDefaultTileMaxBz, t);
+  const int cap = tile_slots == 0 ? tf::kDefaultTileSlotsSmall : tile_slots;
+  if (cap > 0) tf::build_tiling(A->m, A->ap, A->ai, cap, tile_max_bz > 0 ? tile_max_bz : tf::kDefaultTileMaxBz, 512, t);
   *n_tiles = t.tiled ? t.tiles() : 0;
   info[0] = t.bx; info[1] = t.by; info[2] = t.bz; info[3] = (int)(t.reuse * 1000);
   auto dup = [](const std::vector<int> &v) {

@@ -16,6 +16,7 @@ struct tf_schedule {
 namespace tf {
 
 constexpr int kDefaultTileSlots = 800;  // 100 KB of staging per CTA: two CTAs per SM
+constexpr int kDefaultTileSlotsSmall = kDefaultTileSlots;
 constexpr int kDefaultTileMaxBz = 8;
 constexpr int kTileMaxRows = 512;        // rows of a gather tile (16 per 8-lane group of a 256-thread CTA)
 
@@ -48,7 +49,7 @@ struct Tiling {
   double reuse = 0;                       // nonzeros per staged row
   int tiles() const { return tile_row_ptr.empty() ? 0 : (int)tile_row_ptr.size() - 1; }
 };
-int build_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_bz, Tiling &out);
+int build_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_bz, int max_rows, Tiling &out);
 
 // Host-side execution plan (what the planner derives from the patterns).
 struct HostPlan {

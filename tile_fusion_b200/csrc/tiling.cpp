@@ -56,7 +56,7 @@ Lattice detect_lattice(int m, const int *ap, const int *ai) {
 
 }  // namespace
 
-int build_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_bz, Tiling &out) {
+int build_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_bz, int max_rows, Tiling &out) {
   out = Tiling();
   if (slot_cap < 64 || slot_cap > 65535) return TF_OK;
   const Lattice L = detect_lattice(m, ap, ai);
@@ -69,7 +69,7 @@ int build_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_bz, 
   int bx = 0, by = 1, bz = 1;
   double best = 1e30;
   // enough tiles to keep every SM busy several times over
-  const long long max_vol = std::min<long long>(kTileMaxRows, std::max<long long>(64, (long long)m / 1200));
+  const long long max_vol = std::min<long long>(std::min(max_rows, kTileMaxRows), std::max<long long>(64, (long long)m / 1200));
   for (int cx : cand) {
     if (cx < 4 || cx > nx) continue;
     for (int cy : cand) {
