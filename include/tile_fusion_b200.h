@@ -122,6 +122,8 @@ typedef struct {
   int tile_slots;         /* gather tiles: dense-row segments (128 B) a tile may stage in shared
                              memory; 0 = default, <0 = never tile (gather from global memory)      */
   int tile_max_bz;        /* gather tiles: most grid planes a tile may span, 0 = default           */
+  int tile_double_buffer; /* gather tiles: >0 = tiles sized to half the staging buffer so that the copies of
+                             the next column chunk overlap the current one, <0 = full-size tiles, 0 = default */
   int tensor_cores;       /* GeMM-SpMM dense producer: 0 = tcgen05 3xTF32 when the shape allows
                              (K % 4 == 0, N % 16 == 0, N <= 256), <0 = always the fp32 CUDA-core tile */
 } tf_plan_opts;

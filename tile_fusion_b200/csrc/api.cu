@@ -292,8 +292,10 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
   const int slots = o.tile_slots == 0 ? (chain == 1 ? tf::kDefaultTileSlots : tf::kDefaultTileSlotsSmall) : o.tile_slots;
   if (o.mode != TF_MODE_SCHEDULE && slots > 0 && n_cols % 4 == 0) {
     const int max_bz = o.tile_max_bz > 0 ? o.tile_max_bz : tf::kDefaultTileMaxBz;
-    if (F) tf::build_tiling(F->m, F->ap, F->ai, slots, max_bz, tile_rows, pt);
-    tf::build_tiling(A->m, A->ap, A->ai, slots, max_bz, tile_rows, ct);
+    const bool dbl = o.tile_double_buffer > 0 || (o.tile_double_buffer == 0 && tf::kDefaultTileDoubleBuffer);
+    const int cap = dbl ? slots / 2 : slots;  // half-size tiles leave room for the next chunk's copies
+    if (F) tf::build_tiling(F->m, F->ap, F->ai, cap, max_bz, tile_rows, pt);
+    tf::build_tiling(A->m, A->ap, A->ai, cap, max_bz, tile_rows, ct);
     if (pt.tiled || ct.tiled) {
       p->dyn_smem = (size_t)slots * 132;  // 128 B of staging + one source row id per slot
       p->tile_slots = slots;

@@ -269,14 +269,14 @@ __global__ void __launch_bounds__(TILED ? tiled_threads(MODE) : kThreads, TILED 
         return P.inter + (size_t)t * P.n_cols;
       };
       tile_gather<NT, false>(P.pt, rb, P.f_ap, P.f_ax, P.in0, P.n_cols, dst_row, false, 0, 0, 0, stage, hrow,
-                         P.debug_flags);
+                             P.tile_slots, P.debug_flags);
       __syncthreads();
       if (threadIdx.x == 0) publish(P.prod_done, block, P.epoch);
     } else if (TILED && kind == 5) {
       // ---- consume: the rows of one gather tile of the second operator ----
       auto out_row = [&](int r) -> float * { return P.out + (size_t)r * P.n_cols; };
       tile_gather<NT, RING>(P.ct, rb, P.s_ap, P.s_ax, P.inter, P.n_cols, out_row, P.relu != 0, base, P.ring_rows,
-                        P.m_local, stage, hrow, P.debug_flags);
+                        P.m_local, stage, hrow, P.tile_slots, P.debug_flags);
       if (RING) {
         __syncthreads();
         if (threadIdx.x == 0) publish(P.cons_done, block, P.epoch);

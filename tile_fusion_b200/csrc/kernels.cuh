@@ -306,7 +306,8 @@ template <int NT, bool SRC_RING, class DstRow>
 __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, const int *__restrict__ ap,
                                             const float *__restrict__ ax, const float *__restrict__ src,
                                             int n_cols, DstRow dst_row, bool relu, int base, int ring_rows,
-                                            int m_local, float4 *stage, int *hrow, int debug_flags = 0) {
+                                            int m_local, float4 *stage, int *hrow, int stage_slots,
+                                            int debug_flags = 0) {
   const int rp = __ldg(ta.row_ptr + tile), nR = __ldg(ta.row_ptr + tile + 1) - rp;
   const int hp = __ldg(ta.halo_ptr + tile), nH = __ldg(ta.halo_ptr + tile + 1) - hp;
   const int g8 = threadIdx.x >> 3, l8 = threadIdx.x & 7;  // staging: 8 lanes per 128-byte slot
@@ -354,23 +355,43 @@ __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, cons
       if (s < nH) hrow[s] = map_row<SRC_RING>(v[u], base, ring_rows, m_local);
     }
   }
-  for (int c0 = 0; c0 < n_cols; c0 += 32) {
-    __syncthreads();  // hrow is complete; the previous chunk's readers are done with the buffer
-    if (c0 + l8 * 4 < n_cols && !(debug_flags & 2))
+  // When the tile's staged rows fill at most half of the buffer, chunks are double-buffered: the
+  // copies of chunk c + 1 are in flight while chunk c is computed.
+  const bool dbl = 2 * nH <= stage_slots;
+  const int half = dbl ? stage_slots / 2 * 128 : 0;  // byte offset of the second buffer
+  auto issue = [&](int c0, int buf) {
+    if (c0 + l8 * 4 < n_cols && !(debug_flags & 2)) {
+      char *dst = reinterpret_cast<char *>(stage) + buf * half + l8 * 16;
       for (int s = g8; s < nH; s += NT / 8)
-        cp_async16(stage + s * 8 + l8, src + (size_t)hrow[s] * n_cols + c0 + l8 * 4);
-    cp_async_wait_all();
+        cp_async16(dst + s * 128, src + (size_t)hrow[s] * n_cols + c0 + l8 * 4);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  __syncthreads();  // hrow is complete
+  if (dbl) issue(0, 0);
+  int cidx = 0;
+  for (int c0 = 0; c0 < n_cols; c0 += 32, ++cidx) {
+    const int buf = dbl ? (cidx & 1) : 0;
+    if (dbl) {
+      if (c0 + 32 < n_cols) { issue(c0 + 32, buf ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+      else asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+      issue(c0, 0);
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     __syncthreads();
+    const char *bA = sA + buf * half, *bB = sB + buf * half;
 #pragma unroll
     for (int j = 0; j < kTileRowsPerGroup; ++j) {
+      if (j * kTileGroups >= nR) continue;  // uniform over the CTA: no rows left for this round
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         if (k < kshort && !(debug_flags & 1)) {  // uniform over the warp
           const int off = __shfl_sync(kFull, ms[j][k >> 2], k & 3, 4);
           const float v = __shfl_sync(kFull, mv[j][k >> 2], k & 3, 4);
-          const float4 x = *reinterpret_cast<const float4 *>(sA + off);
-          const float4 y = *reinterpret_cast<const float4 *>(sB + off);
+          const float4 x = *reinterpret_cast<const float4 *>(bA + off);
+          const float4 y = *reinterpret_cast<const float4 *>(bB + off);
           if (k < cnt[j]) {
             a.x = fmaf(v, x.x, a.x); a.y = fmaf(v, x.y, a.y); a.z = fmaf(v, x.z, a.z); a.w = fmaf(v, x.w, a.w);
             b.x = fmaf(v, y.x, b.x); b.y = fmaf(v, y.y, b.y); b.z = fmaf(v, y.z, b.z); b.w = fmaf(v, y.w, b.w);
@@ -388,8 +409,8 @@ __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, cons
           for (int k = 0; k < 4; ++k) {
             const int off = __shfl_sync(kFull, s2, k, 4);
             const float v = __shfl_sync(kFull, v2, k, 4);
-            const float4 x = *reinterpret_cast<const float4 *>(sA + off);
-            const float4 y = *reinterpret_cast<const float4 *>(sB + off);
+            const float4 x = *reinterpret_cast<const float4 *>(bA + off);
+            const float4 y = *reinterpret_cast<const float4 *>(bB + off);
             if (q + k < cnt[j]) {
               a.x = fmaf(v, x.x, a.x); a.y = fmaf(v, x.y, a.y); a.z = fmaf(v, x.z, a.z); a.w = fmaf(v, x.w, a.w);
               b.x = fmaf(v, y.x, b.x); b.y = fmaf(v, y.y, b.y); b.z = fmaf(v, y.z, b.z); b.w = fmaf(v, y.w, b.w);
@@ -407,6 +428,7 @@ __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, cons
         if (c0 + colB < n_cols) *reinterpret_cast<float4 *>(o + colB) = b;
       }
     }
+    __syncthreads();  // this chunk's readers are done before its buffer is filled again
   }
 }
 

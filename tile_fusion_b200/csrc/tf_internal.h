@@ -18,6 +18,7 @@ namespace tf {
 constexpr int kDefaultTileSlots = 800;  // 100 KB of staging per CTA: two CTAs per SM
 constexpr int kDefaultTileSlotsSmall = kDefaultTileSlots;
 constexpr int kDefaultTileMaxBz = 8;
+constexpr bool kDefaultTileDoubleBuffer = false;
 constexpr int kTileMaxRows = 512;        // rows of a gather tile (16 per 8-lane group of a 256-thread CTA)
 
 void set_error(const std::string &msg);
