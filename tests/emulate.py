@@ -38,13 +38,17 @@ def run_items(items, info, first, second, C, n_cols, m_local, window=16, seed=0,
     nxt, active = 0, []
     begin, end = info["phase1_begin"], info["end"]
     order = list(range(begin, end))
+    seg_left = {}  # segments of a cut row still to run; the row counts as produced after the last one
+    for t in order:
+        if items[t][0] == 6:
+            seg_left[items[t][2]] = seg_left.get(items[t][2], 0) + 1
     while nxt < len(order) or active:
         while nxt < len(order) and len(active) < window:
             active.append(order[nxt]); nxt += 1
         ready = []
         for t in active:
             kind, block, rb, re, need, base = items[t][:6]
-            wm = pw if kind in (1, 5) else cw
+            wm = pw if kind in (1, 5, 7) else cw
             if need <= wm:
                 ready.append(t)
         assert ready, "deadlock: no in-flight item is ready"
@@ -75,6 +79,27 @@ def run_items(items, info, first, second, C, n_cols, m_local, window=16, seed=0,
             pdone[block] = True
             while pw < n_prod and pdone[pw]:
                 pw += 1
+        elif kind == 6:  # nonzeros [re, base) of row rb, added to T[rb]
+            assert not ring
+            acc = np.zeros(n_cols) if np.isnan(T[rb]).any() else T[rb].copy()
+            for p in range(re, base):
+                acc += np.float64(first[2][p]) * C[first[1][p]]
+            T[rb] = acc
+            seg_left[rb] -= 1
+            if seg_left[rb] == 0:
+                tag[rb] = rb
+            pdone[block] = True
+            while pw < n_prod and pdone[pw]:
+                pw += 1
+        elif kind == 7:  # nonzeros [re, base) of row rb, added to D[rb]
+            assert not ring
+            acc = np.zeros(n_cols) if np.isnan(D[rb]).any() else D[rb].copy()
+            for p in range(re, base):
+                col = second[1][p]
+                if col < m_local:
+                    assert tag[col] == col, "intermediate row read before it was produced"
+                acc += np.float64(second[2][p]) * T[col]
+            D[rb] = acc
         elif kind in (1, 5):
             rows = range(rb, re) if kind == 1 else ctile[1][ctile[0][rb]:ctile[0][rb + 1]]
             if kind == 5:

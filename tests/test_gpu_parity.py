@@ -260,6 +260,57 @@ def test_heavy_row_split_over_cta(torch_cuda, oracle):
     common.assert_close(d, want, "heavy rows")
 
 
+def _hub(n, hubs, seed):
+    rows = [np.arange(hubs[r], dtype=np.int32) if r in hubs else np.unique(np.array([r, (r * 7 + 1) % n], np.int32))
+            for r in range(n)]
+    ap = np.zeros(n + 1, np.int32)
+    ap[1:] = np.cumsum([len(r) for r in rows])
+    ai = np.concatenate(rows)
+    return ap, ai, (synth.uniform(seed, (len(ai),)) - 0.5).astype(np.float32)
+
+
+@pytest.mark.parametrize("n_cols", [128, 47])
+def test_rows_cut_into_segments(torch_cuda, oracle, n_cols):
+    """Rows above the segment size are shared by several CTAs, which add their parts atomically into
+    rows zeroed before the pass; the order of the adds varies, the tolerance covers it."""
+    torch = torch_cuda
+    n = 12000
+    a = _hub(n, {5: 11000, 7000: 9000, 11999: 4097, 300: 700}, 8)
+    A = api.CSRMatrix(n, n, *a)
+    c = synth.uniform(3, (n, n_cols)) - 0.5
+    want = oracle.spmm(*a, oracle.spmm(*a, c))
+    for mode in (api.MODE_STREAM, api.MODE_UNFUSED):
+        plan = api.Plan("spmm_spmm", A, n_cols=n_cols, mode=mode)
+        d = torch.full((n, n_cols), float("nan"), device="cuda")
+        cd = _dev(torch, c)
+        for _ in range(2):  # the second call must start from zeroed rows again
+            plan.spmm_spmm(cd, d)
+            plan.status()
+            common.assert_close(d.cpu().numpy(), want, f"segments SpMM-SpMM mode {mode}")
+        plan.close()
+    dh = np.zeros((n, n_cols), np.float32)
+    api.spMMSpMMExecutor(A, A, api.Matrix(n, n_cols, c), api.Matrix(n, n_cols, dh), None)
+    common.assert_close(dh, want, "segments SpMM-SpMM host")
+    # dense producer, ReLU applied after the atomic adds
+    k = 64
+    b, w = synth.uniform(2, (n, k)) - 0.5, synth.uniform(4, (k, n_cols)) - 0.5
+    want_g = np.maximum(oracle.spmm(*a, (b.astype(np.float64) @ w.astype(np.float64)).astype(np.float32)), 0)
+    plan = api.Plan("gemm_spmm", A, k=k, n_cols=n_cols)
+    d = torch.full((n, n_cols), float("nan"), device="cuda")
+    plan.gemm_spmm(_dev(torch, b), _dev(torch, w), d, relu=True)
+    plan.status()
+    common.assert_close(d.cpu().numpy(), want_g, "segments GeMM-SpMM + ReLU")
+    plan.close()
+    # SDDMM-SpMM
+    q, kk, v = synth.normal(2, (n, 32), 0.125), synth.normal(3, (n, 32), 0.125), synth.normal(4, (n, n_cols), 0.125)
+    want_s = oracle.sddmm_spmm(a, q, kk, v)
+    d = torch.full((n, n_cols), float("nan"), device="cuda")
+    api.sddmmSpMMExecutor(A, api.Matrix(n, 32, _dev(torch, q)), api.Matrix(n, 32, _dev(torch, kk)),
+                          api.Matrix(n, n_cols, _dev(torch, v)), api.Matrix(n, n_cols, d))
+    torch.cuda.synchronize()
+    common.assert_close(d.cpu().numpy(), want_s, "segments SDDMM-SpMM")
+
+
 def test_bounded_wait_reports_timeout(torch_cuda):
     """Failure detection without a GPU fault: consumers of a halo plan are launched without the
     producers they wait for; the wait runs out, the kernel returns and the host reads the status."""

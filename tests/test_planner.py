@@ -67,6 +67,45 @@ def test_heavy_rows_get_their_own_block(built_lib):
     assert cons[:, 3].max() == n and (np.diff(cons[:, 2]) > 0).all()
 
 
+def _hub_matrix(n, hub_rows, seed=3):
+    """Diagonal plus a few rows that touch (almost) every column."""
+    rows = []
+    for r in range(n):
+        if r in hub_rows:
+            rows.append(np.arange(hub_rows[r], dtype=np.int32))
+        else:
+            rows.append(np.unique(np.array([r, (r * 7 + 1) % n], np.int32)))
+    ap = np.zeros(n + 1, np.int32)
+    ap[1:] = np.cumsum([len(r) for r in rows])
+    ai = np.concatenate(rows)
+    ax = (synth.uniform(seed, (len(ai),)) - 0.5).astype(np.float32)
+    return ap, ai, ax
+
+
+@pytest.mark.parametrize("mode", [api.MODE_STREAM, api.MODE_UNFUSED])
+def test_hub_rows_are_cut_into_segments(built_lib, mode):
+    n = 9500
+    t = _hub_matrix(n, {17: 9300, 4000: 5000, 9499: 600})
+    A = api.CSRMatrix(n, n, *t)
+    items, info = api.plan_preview(A, n_cols=2, rows_per_block=64, slack_blocks=2, resident_ctas=12, tile_slots=-1,
+                                   mode=mode)
+    assert info["ring_rows"] == 0
+    for kind, n17, n4000 in ((6, 3, 2), (7, 3, 2)):
+        seg = items[items[:, 0] == kind]
+        assert (seg[:, 2] == 17).sum() == n17 and (seg[:, 2] == 4000).sum() == n4000
+        assert ((seg[:, 5] - seg[:, 3]) <= 4096).all() and ((seg[:, 5] - seg[:, 3]) > 0).all()
+        # the segments of a row cover its nonzeros once
+        s17 = seg[seg[:, 2] == 17]
+        assert s17[0, 3] == t[0][17] and s17[-1, 5] == t[0][18] and (s17[1:, 3] == s17[:-1, 5]).all()
+    whole = items[(items[:, 0] == 1) & (items[:, 2] == 9499)]
+    assert len(whole) == 1 and whole[0, 3] == n  # 600 nonzeros: alone in its block, not cut
+    C = synth.uniform(5, (n, 2)).astype(np.float64)
+    want = _dense_chain(t, C)
+    for seed in range(2):
+        D, _ = run_items(items, info, t, t, C, 2, n, window=12, seed=seed)
+        np.testing.assert_allclose(D, want, rtol=1e-10, atol=1e-10)
+
+
 def test_unfused_mode_lists_all_producers_first(built_lib):
     t = synth.laplacian((12, 12))
     A = _csr(t)

@@ -70,6 +70,7 @@ struct tf_plan {
   bool first_is_second = false;
   tf::HostPlan hp;
   DevBuf<int4> items;
+  DevBuf<int> seg_t, seg_out;  // rows of T / D that are accumulated atomically from segments of a heavy row
   DevBuf<int> prod_done, cons_done;
   DevBuf<tfk::ExecState> state;
   DevBuf<float> inter, sendbuf;
@@ -151,7 +152,21 @@ int upload_items(tf_plan &p) {
     raw[2 * i] = make_int4(it.kind, it.block, it.row_begin, it.row_end);
     raw[2 * i + 1] = make_int4(it.need, it.base, it.aux0, it.aux1);
   }
-  return p.items.upload(raw);
+  int rc = p.items.upload(raw);
+  if (rc == TF_OK && !p.hp.seg_t_rows.empty()) rc = p.seg_t.upload(p.hp.seg_t_rows);
+  if (rc == TF_OK && !p.hp.seg_out_rows.empty()) rc = p.seg_out.upload(p.hp.seg_out_rows);
+  return rc;
+}
+
+// Rows that segments of a heavy row add into start a pass at zero; a final ReLU is applied to them after it.
+int segments_begin(tf_plan &p, const tfk::Params &P, cudaStream_t s) {
+  TF_CUDA(tfk::launch_rows_fix(p.seg_t.p, (int)p.hp.seg_t_rows.size(), p.n_cols, p.inter.p, false, s));
+  TF_CUDA(tfk::launch_rows_fix(p.seg_out.p, (int)p.hp.seg_out_rows.size(), p.n_cols, P.out, false, s));
+  return TF_OK;
+}
+int segments_end(tf_plan &p, const tfk::Params &P, cudaStream_t s) {
+  if (P.relu) TF_CUDA(tfk::launch_rows_fix(p.seg_out.p, (int)p.hp.seg_out_rows.size(), p.n_cols, P.out, true, s));
+  return TF_OK;
 }
 
 int finish_plan(tf_plan &p, const tf_plan_opts &o, int sm_count, bool ring) {
@@ -429,6 +444,10 @@ int run_phases(tf_plan &p, tfk::Params &P, int first_phase, int last_phase, cuda
   if (first_phase <= 1 && last_phase >= 1) ++p.epoch;  // a new pass over the producer blocks
   P.epoch = p.epoch;
   p.launches = 0;
+  if (first_phase <= 1 && last_phase >= 1) {
+    rca = segments_begin(p, P, s);
+    if (rca != TF_OK) return rca;
+  }
   for (int ph = first_phase; ph <= last_phase; ++ph) {
     P.item_begin = p.hp.phase_begin[ph];
     P.item_end = p.hp.phase_begin[ph + 1];
@@ -439,6 +458,7 @@ int run_phases(tf_plan &p, tfk::Params &P, int first_phase, int last_phase, cuda
     TF_CUDA(tfk::launch_stream(p.chain, vec, ch, ring, p.grid, p.dyn_smem, Q, s));
     ++p.launches;
   }
+  if (last_phase == 2) return segments_end(p, P, s);
   return TF_OK;
 }
 
@@ -450,6 +470,7 @@ void build_segments(tf_plan &p, int n_seg) {
   const int n = e - b;
   if (n <= 0 || p.hp.phase_begin[3] != e) return;
   n_seg = std::max(1, std::min(n_seg, n / std::max(1, p.grid)));
+  if (!p.hp.seg_t_rows.empty() || !p.hp.seg_out_rows.empty()) n_seg = 1;  // rows finished by atomic adds: no early copies
   std::vector<int> suffix_min(n + 1, p.m);
   for (int i = n - 1; i >= 0; --i) {
     const tf::Item &it = p.hp.items[b + i];
@@ -494,6 +515,8 @@ int run_host_pipeline(tf_plan &p, tfk::Params &P, const float *h_in, long long i
   P.epoch = p.epoch;
   p.launches = 0;
   long long in_done = 0, out_done = 0;
+  rc = segments_begin(p, P, p.s_run);
+  if (rc != TF_OK) return rc;
   for (int s = 0; s < ns; ++s) {
     const tf_plan::Seg &g = p.segs[s];
     const long long in_to = s == ns - 1 ? in_rows : std::min(in_rows, g.in_rows);
@@ -508,6 +531,10 @@ int run_host_pipeline(tf_plan &p, tfk::Params &P, const float *h_in, long long i
     Q.reset_wm = s == ns - 1;
     TF_CUDA(tfk::launch_stream(p.chain, vec, ch, ring, p.grid, p.dyn_smem, Q, p.s_run));
     ++p.launches;
+    if (s == ns - 1) {
+      rc = segments_end(p, P, p.s_run);
+      if (rc != TF_OK) return rc;
+    }
     TF_CUDA(cudaEventRecord(p.ev_run[s], p.s_run));
     const long long out_to = s == ns - 1 ? p.m : g.out_rows;
     if (out_to > out_done) {
@@ -535,13 +562,15 @@ int run_unfused(tf_plan &p, tfk::Params &P, cudaStream_t s) {
   P.epoch = p.epoch;
   const int np = P.n_prod;
   p.launches = 0;
+  rca = segments_begin(p, P, s);
+  if (rca != TF_OK) return rca;
   tfk::Params Q = P;
   Q.item_begin = 0; Q.item_end = np; Q.reset_wm = 0;
   TF_CUDA(tfk::launch_stream(p.chain, vec, ch, false, p.grid, p.dyn_smem, Q, s));
   Q.item_begin = np; Q.item_end = (int)p.hp.items.size(); Q.reset_wm = 1;
   TF_CUDA(tfk::launch_stream(p.chain, vec, ch, false, p.grid, p.dyn_smem, Q, s));
   p.launches = 2;
-  return TF_OK;
+  return segments_end(p, P, s);
 }
 
 int run_schedule(tf_plan &p, tfk::Params &P, cudaStream_t s) {

@@ -147,6 +147,69 @@ __device__ __forceinline__ void sddmm_row_warp(const Params &P, int row, int lan
   }
 }
 
+// SDDMM-SpMM over the nonzeros [p0, p1) of one heavy row, split over the warps of the CTA; the partial
+// rows are added through shared memory; ATOMIC: the range is one segment of the row, the sum is added to
+// D[row] (zeroed before the pass) with atomicAdd.
+template <int NT, int VEC, int CH, bool ATOMIC>
+__device__ __forceinline__ void sddmm_range_cta(const Params &P, int row, int p0, int p1, float *smem) {
+  constexpr int NW = NT / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int kq = P.k_dim, nv = P.n_cols;
+  const int per = ((p1 - p0 + NW - 1) / NW + 31) / 32 * 32;
+  const int q0 = min(p1, p0 + warp * per), q1 = min(p1, q0 + per);
+  const float *qrow = P.in0 + (size_t)row * kq;
+  constexpr int PANEL = 32 * VEC * CH;
+  for (int col0 = 0; col0 < nv; col0 += PANEL) {
+    float acc[CH][VEC];
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[c][i] = 0.f;
+    for (int p = q0; p < q1; p += 32) {
+      const int cnt = min(32, q1 - p);
+      int col = 0;
+      float val = 0.f;
+      if (lane < cnt) { col = __ldg(P.s_ai + p + lane); val = __ldg(P.s_ax + p + lane); }
+      for (int k = 0; k < cnt; ++k) {
+        const int c = __shfl_sync(kFull, col, k);
+        const float a = __shfl_sync(kFull, val, k);
+        const float *krow = P.in1 + (size_t)c * kq;
+        float part = 0.f;
+        for (int t = lane; t < kq; t += 32) part = fmaf(__ldg(qrow + t), __ldg(krow + t), part);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(kFull, part, o);
+        const float s = part * a;
+        const float *vrow = P.in2 + (size_t)c * nv + col0;
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch) {
+          const int cc = (ch * 32 + lane) * VEC;
+          if (col0 + cc < nv) {
+            float x[VEC];
+            load_vec<VEC, false>(x, vrow + cc);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[ch][i] = fmaf(s, x[i], acc[ch][i]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) smem[warp * PANEL + (c * 32 + lane) * VEC + i] = acc[c][i];
+    __syncthreads();
+    for (int t = threadIdx.x; t < PANEL; t += NT) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) s += smem[w * PANEL + t];
+      if (col0 + t < nv) {
+        if (ATOMIC) atomicAdd(P.out + (size_t)row * nv + col0 + t, s);
+        else P.out[(size_t)row * nv + col0 + t] = s;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // ---------------------------------------------------------------------------
 // The persistent executor
 // ---------------------------------------------------------------------------
@@ -196,7 +259,7 @@ __global__ void __launch_bounds__(TILED ? tiled_threads(MODE) : kThreads, TILED 
 
     if (need > 0) {
       if (warp == 0) {
-        const bool ok = (kind == 1 || kind == 5)
+        const bool ok = (kind == 1 || kind == 5 || kind == 7)
                             ? wait_for(&st->prod_wm, P.prod_done, need, P.epoch, st, P.spin_limit, lane)
                             : wait_for(&st->cons_wm, P.cons_done, need, P.epoch, st, P.spin_limit, lane);
         if (lane == 0) s_ok = ok;
@@ -281,8 +344,24 @@ __global__ void __launch_bounds__(TILED ? tiled_threads(MODE) : kThreads, TILED 
         __syncthreads();
         if (threadIdx.x == 0) publish(P.cons_done, block, P.epoch);
       }
+    } else if (kind == 6) {
+      // ---- one segment of a heavy row of T: nonzeros [re, base), added atomically ----
+      spmm_range_cta<NT, VEC, CH, false, false, true>(P.f_ai, P.f_ax, re, base, P.in0, P.n_cols,
+                                                      P.inter + (size_t)rb * P.n_cols, false, 0, 0, 0, sm.red);
+      __syncthreads();
+      if (threadIdx.x == 0) publish(P.prod_done, block, P.epoch);
+    } else if (kind == 7) {
+      // ---- one segment of a heavy row of D ----
+      spmm_range_cta<NT, VEC, CH, true, false, true>(P.s_ai, P.s_ax, re, base, P.inter, P.n_cols,
+                                                     P.out + (size_t)rb * P.n_cols, false, 0, 0, P.m_local, sm.red);
+    } else if (kind == 8) {
+      // ---- one segment of a heavy SDDMM-SpMM row ----
+      sddmm_range_cta<NT, VEC, CH, true>(P, rb, re, base, sm.red);
     } else if (kind == 2) {
-      // ---- SDDMM-SpMM rows ----
+      // ---- SDDMM-SpMM rows: a heavy row is shared by the CTA, the others go one per warp ----
+      if (re - rb == 1 && __ldg(P.s_ap + re) - __ldg(P.s_ap + rb) >= kHeavyNnz) {
+        sddmm_range_cta<NT, VEC, CH, false>(P, rb, __ldg(P.s_ap + rb), __ldg(P.s_ap + re), sm.red);
+      } else
       for (int r = rb + warp; r < re; r += NW) sddmm_row_warp<VEC, CH>(P, r, lane);
     }
     __syncthreads();
@@ -347,6 +426,16 @@ __global__ void __launch_bounds__(kThreads) schedule_level_kernel(const Params P
                                             P.out + (size_t)r * P.n_cols, P.relu != 0, 0, 0, 0, lane);
       }
     __syncthreads();
+  }
+}
+
+// rows[i] of a row-major matrix set to zero (before a pass that accumulates heavy rows atomically),
+// or clamped at zero (after it, when the chain ends in a ReLU).
+__global__ void rows_fix_kernel(const int *rows, int n_rows, int n_cols, float *x, int relu) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)n_rows * n_cols;
+       i += (long long)gridDim.x * blockDim.x) {
+    float *p = x + (size_t)__ldg(rows + i / n_cols) * n_cols + i % n_cols;
+    *p = relu ? fmaxf(*p, 0.f) : 0.f;
   }
 }
 
@@ -470,6 +559,13 @@ cudaError_t launch_spmm(int vec, int ch, int grid, const int *ap, const int *ai,
                        else spmm_kernel<2, 1><<<grid, kThreads, 0, s>>>(ap, ai, ax, m, x, n_cols, out); }
   else { if (ch == 2) spmm_kernel<1, 2><<<grid, kThreads, 0, s>>>(ap, ai, ax, m, x, n_cols, out);
          else spmm_kernel<1, 1><<<grid, kThreads, 0, s>>>(ap, ai, ax, m, x, n_cols, out); }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rows_fix(const int *rows, int n_rows, int n_cols, float *x, bool relu, cudaStream_t s) {
+  if (n_rows <= 0) return cudaSuccess;
+  const long long total = (long long)n_rows * n_cols;
+  rows_fix_kernel<<<(int)std::min<long long>((total + 255) / 256, 148LL * 8), 256, 0, s>>>(rows, n_rows, n_cols, x, relu ? 1 : 0);
   return cudaGetLastError();
 }
 

@@ -238,17 +238,16 @@ __device__ __forceinline__ void spmm_row_warp(const int *__restrict__ ap, const 
   }
 }
 
-// A row too heavy for one warp: the CTA's warps split its nonzeros and add their partial
-// sums through shared memory (panel by panel).
-template <int NT, int VEC, int CH, bool L2ONLY, bool RING>
-__device__ __forceinline__ void spmm_row_cta(const int *__restrict__ ap, const int *__restrict__ ai,
-                                             const float *__restrict__ ax, int row,
-                                             const float *__restrict__ dense, int n_cols, float *out_row,
-                                             bool relu, int base, int ring_rows, int m_local,
-                                             float *smem /* NT/32 * 32*VEC*CH floats */) {
+// A row too heavy for one warp: the CTA's warps split the nonzeros [p0, p1) of one row and add their
+// partial sums through shared memory (panel by panel).  ATOMIC: the range is one segment of a row cut
+// over several CTAs, the result is added to out_row (zeroed before the pass) with atomicAdd.
+template <int NT, int VEC, int CH, bool L2ONLY, bool RING, bool ATOMIC>
+__device__ __forceinline__ void spmm_range_cta(const int *__restrict__ ai, const float *__restrict__ ax, int p0,
+                                               int p1, const float *__restrict__ dense, int n_cols,
+                                               float *out_row, bool relu, int base, int ring_rows, int m_local,
+                                               float *smem /* NT/32 * 32*VEC*CH floats */) {
   constexpr int NW = NT / 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int p0 = __ldg(ap + row), p1 = __ldg(ap + row + 1);
   const int per = ((p1 - p0 + NW - 1) / NW + 31) / 32 * 32;
   const int q0 = min(p1, p0 + warp * per), q1 = min(p1, q0 + per);
   constexpr int PANEL = 32 * VEC * CH;
@@ -269,10 +268,22 @@ __device__ __forceinline__ void spmm_row_cta(const int *__restrict__ ap, const i
       float s = 0.f;
 #pragma unroll
       for (int w = 0; w < NW; ++w) s += smem[w * PANEL + t];
-      if (col0 + t < n_cols) out_row[col0 + t] = relu ? fmaxf(s, 0.f) : s;
+      if (col0 + t < n_cols) {
+        if (ATOMIC) atomicAdd(out_row + col0 + t, s);
+        else out_row[col0 + t] = relu ? fmaxf(s, 0.f) : s;
+      }
     }
     __syncthreads();
   }
+}
+
+template <int NT, int VEC, int CH, bool L2ONLY, bool RING>
+__device__ __forceinline__ void spmm_row_cta(const int *__restrict__ ap, const int *__restrict__ ai,
+                                             const float *__restrict__ ax, int row,
+                                             const float *__restrict__ dense, int n_cols, float *out_row,
+                                             bool relu, int base, int ring_rows, int m_local, float *smem) {
+  spmm_range_cta<NT, VEC, CH, L2ONLY, RING, false>(ai, ax, __ldg(ap + row), __ldg(ap + row + 1), dense, n_cols, out_row,
+                                                   relu, base, ring_rows, m_local, smem);
 }
 
 // ---------------------------------------------------------------------------

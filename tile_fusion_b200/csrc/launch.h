@@ -18,6 +18,7 @@ cudaError_t launch_schedule_level(int mode, int vec, int ch, int grid, const Par
                                   cudaStream_t s);
 cudaError_t launch_spmm(int vec, int ch, int grid, const int *ap, const int *ai, const float *ax, int m,
                         const float *x, int n_cols, float *out, cudaStream_t s);
+cudaError_t launch_rows_fix(const int *rows, int n_rows, int n_cols, float *x, bool relu, cudaStream_t s);
 cudaError_t launch_fill(bool normal, float *p, long long n, unsigned long long seed, long long off, float sigma,
                         cudaStream_t s);
 }  // namespace tfk

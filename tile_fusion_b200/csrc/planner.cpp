@@ -21,22 +21,38 @@ namespace tf {
 
 namespace {
 
-// consecutive row blocks with at most `rows` rows and `max_nnz` nonzeros (a heavier row stands alone)
-std::vector<int> split_rows(int m, const int *ap, int rows, int max_nnz) {
-  std::vector<int> b{0};
+// Units of the direct path: consecutive row blocks with at most `rows` rows and `max_nnz` nonzeros; a
+// row of kHeavyRowNnz or more nonzeros stands alone; a row above kSegmentNnz is cut into segments.
+std::vector<Unit> split_rows(int m, const int *ap, int rows, int max_nnz) {
+  std::vector<Unit> u;
   int r = 0;
   while (r < m) {
-    int e = r + 1;
-    if (ap) {
-      long long nnz = ap[r + 1] - ap[r];
-      while (e < m && e - r < rows && nnz + (ap[e + 1] - ap[e]) <= max_nnz) { nnz += ap[e + 1] - ap[e]; ++e; }
-    } else {
-      e = std::min(m, r + rows);
+    if (!ap) {
+      const int e = std::min(m, r + rows);
+      u.push_back(Unit{r, e, 0, 0, false});
+      r = e;
+      continue;
     }
-    b.push_back(e);
+    const int len = ap[r + 1] - ap[r];
+    if (len > kSegmentNnz) {
+      const int nseg = (len + kSegmentNnz - 1) / kSegmentNnz, per = (len + nseg - 1) / nseg;
+      for (int s = 0; s < nseg; ++s)
+        u.push_back(Unit{r, r + 1, ap[r] + s * per, std::min(ap[r + 1], ap[r] + (s + 1) * per), true});
+      ++r;
+      continue;
+    }
+    int e = r + 1;
+    if (len < kHeavyRowNnz) {
+      long long nnz = len;
+      while (e < m && e - r < rows && ap[e + 1] - ap[e] < kHeavyRowNnz && nnz + (ap[e + 1] - ap[e]) <= max_nnz) {
+        nnz += ap[e + 1] - ap[e];
+        ++e;
+      }
+    }
+    u.push_back(Unit{r, e, ap[r], ap[e], false});
     r = e;
   }
-  return b;
+  return u;
 }
 
 inline int block_of(const std::vector<int> &bounds, int row) {
@@ -52,12 +68,17 @@ int build_stream_plan(const PlanParams &pp, const int *first_ap, const int *firs
   const bool p_tiled = ptile && ptile->tiled, c_tiled = ctile && ctile->tiled;
 
   // ---- units: gather tiles where the operator is tiled, consecutive row blocks otherwise ----
-  out.prod_rows.clear();
-  out.cons_rows.clear();
-  if (!p_tiled) out.prod_rows = split_rows(m, pp.producer_is_gemm ? nullptr : first_ap, rb, pp.max_block_nnz);
-  if (!c_tiled) out.cons_rows = split_rows(m, sec_ap, rb, pp.max_block_nnz);
-  const int np = p_tiled ? ptile->tiles() : (int)out.prod_rows.size() - 1;
-  const int nc = c_tiled ? ctile->tiles() : (int)out.cons_rows.size() - 1;
+  out.prod_units.clear();
+  out.cons_units.clear();
+  out.seg_t_rows.clear();
+  out.seg_out_rows.clear();
+  if (!p_tiled) out.prod_units = split_rows(m, pp.producer_is_gemm ? nullptr : first_ap, rb, pp.max_block_nnz);
+  if (!c_tiled) out.cons_units = split_rows(m, sec_ap, rb, pp.max_block_nnz);
+  const int np = p_tiled ? ptile->tiles() : (int)out.prod_units.size();
+  const int nc = c_tiled ? ctile->tiles() : (int)out.cons_units.size();
+  bool any_seg = false;
+  for (const Unit &u : out.prod_units) if (u.seg) { any_seg = true; if (out.seg_t_rows.empty() || out.seg_t_rows.back() != u.r0) out.seg_t_rows.push_back(u.r0); }
+  for (const Unit &u : out.cons_units) if (u.seg) { any_seg = true; if (out.seg_out_rows.empty() || out.seg_out_rows.back() != u.r0) out.seg_out_rows.push_back(u.r0); }
   out.n_prod = np;
   out.n_cons = nc;
 
@@ -69,8 +90,9 @@ int build_stream_plan(const PlanParams &pp, const int *first_ap, const int *firs
         prod_of_row[r] = j; pmin[j] = std::min(pmin[j], r); pmax[j] = std::max(pmax[j], r);
       }
     } else {
-      for (int r = out.prod_rows[j]; r < out.prod_rows[j + 1]; ++r) prod_of_row[r] = j;
-      pmin[j] = out.prod_rows[j]; pmax[j] = out.prod_rows[j + 1] - 1;
+      // the last segment of a cut row stands for the row: waiting for it waits for every earlier unit
+      for (int r = out.prod_units[j].r0; r < out.prod_units[j].r1; ++r) prod_of_row[r] = j;
+      pmin[j] = out.prod_units[j].r0; pmax[j] = out.prod_units[j].r1 - 1;
     }
   }
   // what every consumer unit reads: lowest / highest local row, last producer unit, any halo row
@@ -86,7 +108,9 @@ int build_stream_plan(const PlanParams &pp, const int *first_ap, const int *firs
     if (c_tiled) {
       for (int k = ctile->tile_halo_ptr[c]; k < ctile->tile_halo_ptr[c + 1]; ++k) see(c, ctile->halo[k]);
     } else {
-      for (int r = out.cons_rows[c]; r < out.cons_rows[c + 1]; ++r)
+      const Unit &u = out.cons_units[c];
+      if (u.seg) { for (int j = u.p0; j < u.p1; ++j) see(c, sec_ai[j]); }
+      else for (int r = u.r0; r < u.r1; ++r)
         for (int j = sec_ap[r]; j < sec_ap[r + 1]; ++j) see(c, sec_ai[j]);
     }
   }
@@ -98,13 +122,17 @@ int build_stream_plan(const PlanParams &pp, const int *first_ap, const int *firs
     int mx = 0;
     if (pp.producer_is_gemm) mx = pmax[j];
     else if (p_tiled) { for (int k = ptile->tile_halo_ptr[j]; k < ptile->tile_halo_ptr[j + 1]; ++k) mx = std::max(mx, ptile->halo[k]); }
-    else { for (int r = out.prod_rows[j]; r < out.prod_rows[j + 1]; ++r) for (int q = first_ap[r]; q < first_ap[r + 1]; ++q) mx = std::max(mx, first_ai[q]); }
+    else {
+      const Unit &u = out.prod_units[j];
+      const int q0 = u.seg ? u.p0 : first_ap[u.r0], q1 = u.seg ? u.p1 : first_ap[u.r1];
+      for (int q = q0; q < q1; ++q) mx = std::max(mx, first_ai[q]);
+    }
     psrc_max[j] = mx;
   }
   for (int c = 0; c < nc; ++c) {
     int mn = INT_MAX;
     if (c_tiled) { for (int k = ctile->tile_row_ptr[c]; k < ctile->tile_row_ptr[c + 1]; ++k) mn = std::min(mn, ctile->rows[k]); }
-    else mn = out.cons_rows[c];
+    else mn = out.cons_units[c].r0;
     cout_min[c] = mn == INT_MAX ? 0 : mn;
   }
 
@@ -133,7 +161,7 @@ int build_stream_plan(const PlanParams &pp, const int *first_ap, const int *firs
 
   // ---- ring: large enough that a producer never overwrites a row a listed-later consumer reads ----
   long long ring_rows = 0;
-  if (pp.ring_bytes > 0 && !multi) {
+  if (pp.ring_bytes > 0 && !multi && !any_seg) {
     // A producer should find its slot free without waiting: count as finished only the consumers
     // listed at least `lag` tickets before it (about one ticket per resident CTA).
     const int lag = 2 * slack + 2;
@@ -160,10 +188,13 @@ int build_stream_plan(const PlanParams &pp, const int *first_ap, const int *firs
     Item it{};
     it.kind = c_tiled ? ITEM_CONSUME_TILED : ITEM_CONSUME;
     it.block = c;
-    it.row_begin = c_tiled ? c : out.cons_rows[c];
-    it.row_end = c_tiled ? c + 1 : out.cons_rows[c + 1];
+    it.row_begin = c_tiled ? c : out.cons_units[c].r0;
+    it.row_end = c_tiled ? c + 1 : out.cons_units[c].r1;
     it.need = need[c];
     it.base = (ring_rows && cmin[c] != INT_MAX) ? (int)((cmin[c] / ring_rows) * ring_rows) : 0;
+    if (!c_tiled && out.cons_units[c].seg) {
+      it.kind = ITEM_CONSUME_SEG; it.row_end = out.cons_units[c].p0; it.base = out.cons_units[c].p1;
+    }
     it.aux1 = cout_min[c];  // lowest output row this unit writes
     out.items.push_back(it);
   };
@@ -173,9 +204,12 @@ int build_stream_plan(const PlanParams &pp, const int *first_ap, const int *firs
     Item it{};
     it.kind = p_tiled ? ITEM_PRODUCE_TILED : ITEM_PRODUCE;
     it.block = j;
-    it.row_begin = p_tiled ? j : out.prod_rows[j];
-    it.row_end = p_tiled ? j + 1 : out.prod_rows[j + 1];
+    it.row_begin = p_tiled ? j : out.prod_units[j].r0;
+    it.row_end = p_tiled ? j + 1 : out.prod_units[j].r1;
     it.base = ring_rows ? (int)((pmin[j] / ring_rows) * ring_rows) : 0;
+    if (!p_tiled && out.prod_units[j].seg) {
+      it.kind = ITEM_PRODUCE_SEG; it.row_end = out.prod_units[j].p0; it.base = out.prod_units[j].p1;
+    }
     it.aux0 = psrc_max[j];  // highest row of the producer's dense input this unit reads
     if (ring_rows) {
       // consumers that still read the rows this unit overwrites: those with sufmin <= pmax - ring
@@ -194,16 +228,23 @@ int build_stream_plan(const PlanParams &pp, const int *first_ap, const int *firs
 }
 
 int build_single_pass_plan(const PlanParams &pp, const int *ap, HostPlan &out) {
-  out.prod_rows.clear();
-  out.cons_rows = split_rows(pp.m, ap, pp.rows_per_block, pp.max_block_nnz);
-  const int nc = (int)out.cons_rows.size() - 1;
+  out.prod_units.clear();
+  out.seg_t_rows.clear();
+  out.seg_out_rows.clear();
+  out.cons_units = split_rows(pp.m, ap, pp.rows_per_block, pp.max_block_nnz);
+  const int nc = (int)out.cons_units.size();
   out.n_prod = 0;
   out.n_cons = nc;
   out.items.clear();
   for (int c = 0; c < nc; ++c) {
     Item it{};
     it.kind = ITEM_SDDMM; it.block = c;
-    it.row_begin = out.cons_rows[c]; it.row_end = out.cons_rows[c + 1];
+    const Unit &u = out.cons_units[c];
+    it.row_begin = u.r0; it.row_end = u.r1;
+    if (u.seg) {
+      it.kind = ITEM_SDDMM_SEG; it.row_end = u.p0; it.base = u.p1;
+      if (out.seg_out_rows.empty() || out.seg_out_rows.back() != u.r0) out.seg_out_rows.push_back(u.r0);
+    }
     out.items.push_back(it);
   }
   out.phase_begin[0] = out.phase_begin[1] = 0;

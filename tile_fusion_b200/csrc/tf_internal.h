@@ -18,6 +18,8 @@ namespace tf {
 constexpr int kDefaultTileSlots = 800;  // 100 KB of staging per CTA: two CTAs per SM
 constexpr int kDefaultTileSlotsSmall = kDefaultTileSlots;
 constexpr int kDefaultTileMaxBz = 8;
+constexpr int kHeavyRowNnz = 512;    // a row at least this long is a block of its own (the CTA's warps share it)
+constexpr int kSegmentNnz = 4096;    // a row longer than this is cut into segments run by different CTAs
 constexpr bool kDefaultTileDoubleBuffer = false;
 constexpr int kTileMaxRows = 512;        // rows of a gather tile (16 per 8-lane group of a 256-thread CTA)
 
@@ -28,7 +30,9 @@ int fail(int code, const std::string &msg);
 enum ItemKind : int {
   ITEM_PRODUCE = 0, ITEM_CONSUME = 1, ITEM_SDDMM = 2, ITEM_SEND = 3,
   ITEM_PRODUCE_TILED = 4,  // row_begin = tile index of the first operator's tiling
-  ITEM_CONSUME_TILED = 5   // row_begin = tile index of the second operator's tiling
+  ITEM_CONSUME_TILED = 5,  // row_begin = tile index of the second operator's tiling
+  // heavy-row segments: row_begin = row, row_end = first nonzero, base = one past the last nonzero
+  ITEM_PRODUCE_SEG = 6, ITEM_CONSUME_SEG = 7, ITEM_SDDMM_SEG = 8
 };
 struct Item {
   int kind;       // ItemKind
@@ -52,10 +56,19 @@ struct Tiling {
 };
 int build_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_bz, int max_rows, Tiling &out);
 
+// A unit of the direct (untiled) path: rows [r0, r1), or -- for a row too heavy for one CTA -- the
+// nonzeros [p0, p1) of the single row r0 (seg), whose partial sums are added atomically.
+struct Unit {
+  int r0, r1, p0, p1;
+  bool seg;
+};
+
 // Host-side execution plan (what the planner derives from the patterns).
 struct HostPlan {
-  std::vector<int> prod_rows;  // producer block boundaries (size blocks + 1); empty when tiled
-  std::vector<int> cons_rows;  // consumer block boundaries; empty when tiled
+  std::vector<Unit> prod_units;  // producer row blocks / heavy-row segments; empty when tiled
+  std::vector<Unit> cons_units;  // consumer row blocks / heavy-row segments; empty when tiled
+  std::vector<int> seg_t_rows;   // rows of T accumulated from segments (zeroed before a pass)
+  std::vector<int> seg_out_rows; // rows of D accumulated from segments (zeroed before, ReLU after)
   int n_prod = 0, n_cons = 0;  // units (blocks or tiles) on each side
   std::vector<Item> items;     // all items in ticket order
   int phase_begin[4] = {0, 0, 0, 0};  // item ranges of the three phases
