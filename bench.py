@@ -276,6 +276,7 @@ def main():
     ap.add_argument("--tile-slots", type=int, default=0)
     ap.add_argument("--tile-max-bz", type=int, default=0)
     ap.add_argument("--tile-double", type=int, default=0)
+    ap.add_argument("--tile-pipeline", type=int, default=0, help="<0: run gather tiles on the two-CTA kernel")
     ap.add_argument("--dims", default="", help="override the per-rank grid, e.g. 128,128,32 (profiling on a small case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -319,7 +320,7 @@ def main():
     st = torch.cuda.current_stream().cuda_stream
     mode = api.MODE_STREAM if args.mode == "stream" else api.MODE_UNFUSED
     plan_kw = dict(rows_per_block=args.rows_per_block, slack_blocks=args.slack, ctas_per_sm=args.ctas_per_sm,
-                   tile_slots=args.tile_slots, tile_max_bz=args.tile_max_bz, tile_double_buffer=args.tile_double,
+                   tile_slots=args.tile_slots, tile_max_bz=args.tile_max_bz, tile_double_buffer=args.tile_double, tile_pipeline=args.tile_pipeline,
                    ring_bytes=args.ring_mb << 20 if args.ring_mb > 0 else (0 if args.ring_mb == 0 else -1))
 
     def fill(t, seed, offset):

@@ -126,6 +126,9 @@ typedef struct {
                              the next column chunk overlap the current one, <0 = full-size tiles, 0 = default */
   int tensor_cores;       /* GeMM-SpMM dense producer: 0 = tcgen05 3xTF32 when the shape allows
                              (K % 4 == 0, N % 16 == 0, N <= 256), <0 = always the fp32 CUDA-core tile */
+  int tile_pipeline;      /* SpMM-SpMM with both operators tiled and no ring requested: 0 = run the tiles on
+                             the role-split pipeline (one CTA per SM: staging warps copy the next column
+                             chunk while compute warps work on the current one), <0 = never              */
 } tf_plan_opts;
 
 typedef struct tf_plan tf_plan;

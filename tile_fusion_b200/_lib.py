@@ -33,7 +33,8 @@ class PlanOpts(C.Structure):
     _fields_ = [("mode", C.c_int), ("rows_per_block", C.c_int), ("ring_bytes", C.c_int),
                 ("slack_blocks", C.c_int), ("ctas_per_sm", C.c_int), ("halo_rows", C.c_int),
                 ("n_boundary", C.c_int), ("boundary_rows", C.c_void_p), ("tile_slots", C.c_int),
-                ("tile_max_bz", C.c_int), ("tile_double_buffer", C.c_int), ("tensor_cores", C.c_int)]
+                ("tile_max_bz", C.c_int), ("tile_double_buffer", C.c_int), ("tensor_cores", C.c_int),
+                ("tile_pipeline", C.c_int)]
 
 
 EXPORTS = [

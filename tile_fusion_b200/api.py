@@ -187,14 +187,14 @@ class Plan:
                  mode: int = MODE_STREAM, schedule: FusedSchedule | None = None, rows_per_block: int = 0,
                  ring_bytes: int = 0, slack_blocks: int = -1, ctas_per_sm: int = 0, halo_rows: int = 0,
                  boundary_rows=None, tile_slots: int = 0, tile_max_bz: int = 0, tensor_cores: int = 0,
-                 tile_double_buffer: int = 0):
+                 tile_double_buffer: int = 0, tile_pipeline: int = 0):
         L = _lib.lib()
         self.chain, self.A, self.B = chain, A, B
         self.n_cols, self.k = int(n_cols), int(k)
         br = _i32(boundary_rows) if boundary_rows is not None and len(boundary_rows) else None
         o = _lib.PlanOpts(mode, rows_per_block, ring_bytes, slack_blocks, ctas_per_sm, halo_rows,
                           0 if br is None else br.shape[0], None if br is None else br.ctypes.data,
-                          tile_slots, tile_max_bz, tile_double_buffer, tensor_cores)
+                          tile_slots, tile_max_bz, tile_double_buffer, tensor_cores, tile_pipeline)
         h = C.c_void_p()
         ca = A._c()
         sh = schedule._h if schedule is not None else None
@@ -375,7 +375,7 @@ def plan_preview(A: CSRMatrix, B: CSRMatrix | None = None, *, producer_is_gemm=F
     {kind, block, row_begin, row_end, need, base, aux0, aux1}, plus an info dict."""
     br = _i32(boundary_rows) if boundary_rows is not None and len(boundary_rows) else None
     o = _lib.PlanOpts(mode, rows_per_block, ring_bytes, slack_blocks, 0, halo_rows,
-                      0 if br is None else br.shape[0], None if br is None else br.ctypes.data, tile_slots, tile_max_bz, 0, 0)
+                      0 if br is None else br.shape[0], None if br is None else br.ctypes.data, tile_slots, tile_max_bz, 0, 0, 0)
     ca = A._c()
     cb = B._c() if B is not None else None
     items, n = C.c_void_p(), C.c_longlong()

@@ -77,12 +77,27 @@ struct tf_plan {
   // gather tiles (stream / unfused mode)
   struct DevTiling {
     DevBuf<int> row_ptr, rows, halo_ptr, halo;
-    DevBuf<unsigned short> slot;
+    DevBuf<unsigned short> slot, eslot;
+    DevBuf<int> ecnt;
+    DevBuf<float> eval;
     bool on = false;
-    int upload(const tf::Tiling &t) {
+    // ap, ax: host CSR of the operator the tiling belongs to
+    int upload(const tf::Tiling &t, const int *ap, const float *ax) {
       on = t.tiled;
       if (!on) return TF_OK;
-      int rc = row_ptr.upload(t.tile_row_ptr);
+      const size_t nr = t.rows.size();
+      std::vector<int> cnt(nr);
+      std::vector<unsigned short> es(nr * 8, 0);
+      std::vector<float> ev(nr * 8, 0.f);
+      for (size_t e = 0; e < nr; ++e) {
+        const int r = t.rows[e];
+        cnt[e] = ap[r + 1] - ap[r];
+        for (int k = 0; k < std::min(cnt[e], 8); ++k) { es[e * 8 + k] = t.slot[ap[r] + k]; ev[e * 8 + k] = ax[ap[r] + k]; }
+      }
+      int rc = ecnt.upload(cnt);
+      if (rc == TF_OK) rc = eslot.upload(es);
+      if (rc == TF_OK) rc = eval.upload(ev);
+      if (rc == TF_OK) rc = row_ptr.upload(t.tile_row_ptr);
       if (rc == TF_OK) rc = rows.upload(t.rows);
       if (rc == TF_OK) rc = halo_ptr.upload(t.tile_halo_ptr);
       if (rc == TF_OK) rc = halo.upload(t.halo);
@@ -90,13 +105,15 @@ struct tf_plan {
       return rc;
     }
     tfk::TileArrays view() const {
-      tfk::TileArrays a{nullptr, nullptr, nullptr, nullptr, nullptr};
-      if (on) a = tfk::TileArrays{row_ptr.p, rows.p, halo_ptr.p, halo.p, slot.p};
+      tfk::TileArrays a{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+      if (on) a = tfk::TileArrays{row_ptr.p, rows.p, halo_ptr.p, halo.p, slot.p, ecnt.p, eslot.p, eval.p};
       return a;
     }
   } ptile, ctile;
   size_t dyn_smem = 0;
   int tile_slots = 0;
+  bool pipe = false;  // every item of phases 1 and 2 is a gather tile: run them on the tile pipeline
+  int pipe_grid = 0;
   // tensor-core dense producer
   bool use_tc = false;
   DevBuf<float> w_hi, w_lo;  // split, transposed weight [n_cols][k]
@@ -145,12 +162,21 @@ int default_rows_per_block(int n_cols, bool gemm) {
   return n_cols >= 128 ? 64 : 128;
 }
 
-int upload_items(tf_plan &p) {
+// pt, ct: the gather tiles of a plan the tile pipeline runs; its tile items carry the extents of the
+// tile ({kind, flag, tile, rows} {need, staged rows, offset of the staged rows, offset of the rows}),
+// so that the kernel needs no further lookup before it can start on a tile.
+int upload_items(tf_plan &p, const tf::Tiling *pt = nullptr, const tf::Tiling *ct = nullptr) {
   std::vector<int4> raw(2 * p.hp.items.size());
   for (size_t i = 0; i < p.hp.items.size(); ++i) {
     const tf::Item &it = p.hp.items[i];
     raw[2 * i] = make_int4(it.kind, it.block, it.row_begin, it.row_end);
     raw[2 * i + 1] = make_int4(it.need, it.base, it.aux0, it.aux1);
+    if (p.pipe && (it.kind == tf::ITEM_PRODUCE_TILED || it.kind == tf::ITEM_CONSUME_TILED)) {
+      const tf::Tiling &t = it.kind == tf::ITEM_PRODUCE_TILED ? *pt : *ct;
+      const int k = it.row_begin;
+      raw[2 * i].w = t.tile_row_ptr[k + 1] - t.tile_row_ptr[k];
+      raw[2 * i + 1] = make_int4(it.need, t.tile_halo_ptr[k + 1] - t.tile_halo_ptr[k], t.tile_halo_ptr[k], t.tile_row_ptr[k]);
+    }
   }
   int rc = p.items.upload(raw);
   if (rc == TF_OK && !p.hp.seg_t_rows.empty()) rc = p.seg_t.upload(p.hp.seg_t_rows);
@@ -334,13 +360,22 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
     if (rc != TF_OK) return rc;
     pp.max_ctas = p->grid;
   }
+  // both operators tiled: the tile pipeline runs the chain (one CTA per SM, about three tiles in flight
+  // each); it has no ring addressing, so a ring is only kept when the caller asked for one
+  const bool want_pipe = chain == 0 && pt.tiled && ct.tiled && o.tile_pipeline >= 0 && o.ring_bytes <= 0 &&
+                         tfk::tile_pipeline_smem(p->tile_slots) > 0 && tfk::tile_pipeline_smem(p->tile_slots) <= 225 * 1024;
+  if (want_pipe) { pp.ring_bytes = -1; pp.max_ctas = 4 * sm_count; }
   p->tile_info[0] = pt.bx; p->tile_info[1] = pt.by; p->tile_info[2] = pt.bz; p->tile_info[3] = pt.tiles();
   p->tile_info[4] = ct.bx; p->tile_info[5] = ct.by; p->tile_info[6] = ct.bz; p->tile_info[7] = ct.tiles();
   rc = tf::build_stream_plan(pp, F ? F->ap : nullptr, F ? F->ai : nullptr, A->ap, A->ai, &pt, &ct, p->hp);
   if (rc != TF_OK) return rc;
-  rc = p->ptile.upload(pt);
-  if (rc == TF_OK) rc = p->ctile.upload(ct);
+  rc = p->ptile.upload(pt, F ? F->ap : nullptr, F ? F->ax : nullptr);
+  if (rc == TF_OK) rc = p->ctile.upload(ct, A->ap, A->ax);
   if (rc != TF_OK) return rc;
+  p->pipe = want_pipe && p->hp.ring_rows == 0;
+  for (int i = p->hp.phase_begin[1]; p->pipe && i < p->hp.phase_begin[3]; ++i)
+    p->pipe = p->hp.items[i].kind == tf::ITEM_PRODUCE_TILED || p->hp.items[i].kind == tf::ITEM_CONSUME_TILED;
+  p->pipe_grid = (o.halo_rows > 0 || o.n_boundary > 0) ? std::max(1, sm_count - 8) : sm_count;
   rc = finish_plan(*p, o, sm_count, p->hp.ring_rows > 0);
   if (rc != TF_OK) return rc;
 
@@ -369,7 +404,7 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
     if (rc != TF_OK) return rc;
   }
   if (o.mode == TF_MODE_STREAM && !o.halo_rows && !o.n_boundary) build_segments(*p, 16);
-  rc = upload_items(*p);
+  rc = upload_items(*p, &pt, &ct);
   if (rc == TF_OK) rc = zero_state(*p);
   if (rc == TF_OK) rc = p->inter.alloc((size_t)p->hp.inter_rows * n_cols);
   if (rc != TF_OK) return rc;
@@ -432,6 +467,12 @@ int prepare_tc(tf_plan &p, tfk::Params &P, cudaStream_t s) {
   return TF_OK;
 }
 
+// One launch over the items [Q.item_begin, Q.item_end) of phases 1 and 2.
+cudaError_t launch_items(tf_plan &p, int vec, int ch, bool ring, const tfk::Params &Q, cudaStream_t s) {
+  if (p.pipe) return tfk::launch_tile_pipeline(p.pipe_grid, p.tile_slots, Q, s);
+  return tfk::launch_stream(p.chain, vec, ch, ring, p.grid, p.dyn_smem, Q, s);
+}
+
 int run_phases(tf_plan &p, tfk::Params &P, int first_phase, int last_phase, cudaStream_t s) {
   int vec, ch;
   call_shape(p, {P.in0, P.in1, P.in2, P.out}, &vec, &ch);
@@ -455,7 +496,8 @@ int run_phases(tf_plan &p, tfk::Params &P, int first_phase, int last_phase, cuda
     tfk::Params Q = P;
     if (ph == 0) Q.inter = p.sendbuf.p;
     Q.reset_wm = (ph == 2) || (ph == 1 && p.hp.phase_begin[3] == p.hp.phase_begin[2] && last_phase >= 1);
-    TF_CUDA(tfk::launch_stream(p.chain, vec, ch, ring, p.grid, p.dyn_smem, Q, s));
+    if (ph == 0) TF_CUDA(tfk::launch_stream(p.chain, vec, ch, ring, p.grid, p.dyn_smem, Q, s));
+    else TF_CUDA(launch_items(p, vec, ch, ring, Q, s));
     ++p.launches;
   }
   if (last_phase == 2) return segments_end(p, P, s);
@@ -529,7 +571,7 @@ int run_host_pipeline(tf_plan &p, tfk::Params &P, const float *h_in, long long i
     tfk::Params Q = P;
     Q.item_begin = g.item_begin; Q.item_end = g.item_end;
     Q.reset_wm = s == ns - 1;
-    TF_CUDA(tfk::launch_stream(p.chain, vec, ch, ring, p.grid, p.dyn_smem, Q, p.s_run));
+    TF_CUDA(launch_items(p, vec, ch, ring, Q, p.s_run));
     ++p.launches;
     if (s == ns - 1) {
       rc = segments_end(p, P, p.s_run);
@@ -566,9 +608,9 @@ int run_unfused(tf_plan &p, tfk::Params &P, cudaStream_t s) {
   if (rca != TF_OK) return rca;
   tfk::Params Q = P;
   Q.item_begin = 0; Q.item_end = np; Q.reset_wm = 0;
-  TF_CUDA(tfk::launch_stream(p.chain, vec, ch, false, p.grid, p.dyn_smem, Q, s));
+  TF_CUDA(launch_items(p, vec, ch, false, Q, s));
   Q.item_begin = np; Q.item_end = (int)p.hp.items.size(); Q.reset_wm = 1;
-  TF_CUDA(tfk::launch_stream(p.chain, vec, ch, false, p.grid, p.dyn_smem, Q, s));
+  TF_CUDA(launch_items(p, vec, ch, false, Q, s));
   p.launches = 2;
   return segments_end(p, P, s);
 }
@@ -655,8 +697,8 @@ int tf_plan_info(const tf_plan *p, long long info[8]) {
   info[1] = p->hp.n_prod;
   info[2] = p->hp.n_cons;
   info[3] = p->hp.ring_rows;
-  info[4] = p->grid;
-  info[5] = p->dyn_smem > 0 ? tfk::tiled_threads(p->chain) : tfk::kThreads;
+  info[4] = p->pipe ? p->pipe_grid : p->grid;
+  info[5] = p->pipe ? 672 : (p->dyn_smem > 0 ? tfk::tiled_threads(p->chain) : tfk::kThreads);
   info[6] = p->launches;
   info[7] = p->hp.inter_rows;
   return TF_OK;

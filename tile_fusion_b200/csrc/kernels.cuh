@@ -36,6 +36,11 @@ struct ExecState {
 struct TileArrays {
   const int *row_ptr, *rows, *halo_ptr, *halo;
   const unsigned short *slot;
+  // in tile-row order (index row_ptr[tile] + i): the row's length and its first 8 (slot, value) pairs,
+  // padded with slot 0 / value 0
+  const int *ecnt;
+  const unsigned short *eslot;
+  const float *eval;
 };
 
 struct Params {

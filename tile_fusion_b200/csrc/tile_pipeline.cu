@@ -1,0 +1,305 @@
+// Gather-tile pipeline: the persistent executor for plans whose items are all gather tiles.
+//
+// One CTA per SM, split into roles.  A control warp takes the tickets, waits (bounded) for the
+// producer tiles an item depends on and posts a tile descriptor, up to four tiles ahead of the
+// others, so the latency of the ticket, the item record and the flag checks stays off the data
+// path.  Four staging warps copy the tile's source rows -- one 32-column chunk (128 bytes per row)
+// at a time -- into one of two shared-memory buffers with 16-byte asynchronous copies whose
+// completion is counted by an mbarrier.  Sixteen compute warps wait for a full
+// buffer, form the tile's output rows for that chunk from shared memory, store them, and hand
+// the buffer back.  Copies for chunk g + 1 (of this or of the next tile) are therefore in
+// flight while chunk g is computed, and neither side ever meets the other at a CTA barrier.
+//
+// Every wait is bounded: a wait that runs out sets the sticky error flag of the launch and the
+// thread leaves its loop; the others then run out of their own waits and follow.
+#include "kernels.cuh"
+#include "gemm_tc.cuh"  // mbarrier helpers
+#include "launch.h"
+
+namespace tfk {
+
+namespace {
+
+constexpr int kPipeCompute = 512;  // 16 compute warps: 4 lanes per row, up to 4 rows per lane group
+constexpr int kPipeStagers = 128;  // 4 staging warps: 8 lanes per 128-byte slot, 16 slots per step
+constexpr int kPipeThreads = kPipeCompute + kPipeStagers + 32;  // + the control warp
+constexpr int kPipeDepth = 4;      // tile descriptors in flight
+constexpr int kPipeReaders = (kPipeCompute + kPipeStagers) / 32;  // warps that read every descriptor
+constexpr int kPipeGroups = kPipeCompute / 4;
+constexpr int kPipeIdRegs = 7;     // source row ids per staging lane: 7 * 8 steps * 16 slot groups = 896 slots
+constexpr int kPipeMaxSlots = kPipeIdRegs * 8 * 16;
+
+struct PipeShared {
+  unsigned long long full[2];            // a chunk buffer holds its copies (one arrival per staging thread)
+  unsigned long long empty[2];           // its readers are done (one arrival per compute warp)
+  unsigned long long desc_bar[kPipeDepth];   // descriptor posted (control warp)
+  unsigned long long desc_free[kPipeDepth];  // every reader warp has copied it
+  int desc[kPipeDepth][8];               // kind (-1: no more work), flag index, tile, nR, nH, hp, rp, -
+  int done_cnt[kPipeDepth];              // compute warps that finished the tile
+};
+
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// bounded wait with a warp-uniform answer (the callers run warp collectives afterwards)
+__device__ int g_pipe_sleep = 0;  // diagnostics: back off between polls
+__device__ __forceinline__ bool warp_wait(unsigned long long *bar, unsigned parity, int limit) {
+  const int ns = g_pipe_sleep;
+  if (ns == 0) return __all_sync(kFull, mbar_wait(bar, parity, limit));
+  bool done = false;
+  for (int i = 0; i < limit && !done; ++i) {
+    done = mbar_wait(bar, parity, 1);
+    if (!done) __nanosleep(ns);
+  }
+  return __all_sync(kFull, done);
+}
+// arrives once every asynchronous copy this thread issued so far has landed
+__device__ __forceinline__ void cp_async_arrive(unsigned long long *bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __grid_constant__ Params P) {
+  extern __shared__ float4 stage[];  // two buffers of tile_slots * 128 bytes
+  __shared__ PipeShared sh;
+  const int tid = threadIdx.x, lane = tid & 31;
+  ExecState *st = P.st;
+  const int n_items = P.item_end - P.item_begin;
+  const int nchunks = (P.n_cols + 31) / 32;
+  const int buf_bytes = P.tile_slots * 128;
+  const int limit = P.spin_limit;
+  if (tid == 0) {
+    for (int b = 0; b < 2; ++b) { mbar_init(&sh.full[b], kPipeStagers); mbar_init(&sh.empty[b], kPipeCompute / 32); }
+    for (int i = 0; i < kPipeDepth; ++i) {
+      mbar_init(&sh.desc_bar[i], 1);
+      mbar_init(&sh.desc_free[i], kPipeReaders);
+      sh.done_cnt[i] = 0;
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (tid >= kPipeCompute + kPipeStagers) {
+    // ------------------------------------------------------------------ control warp
+    int nxt = 0;
+    if (lane == 0) nxt = atomicAdd(&st->ticket, 1);
+    bool ok = true;
+    for (int t = 0;; ++t) {
+      const int slot = t & (kPipeDepth - 1);
+      if (t >= kPipeDepth && !warp_wait(&sh.desc_free[slot], (t / kPipeDepth - 1) & 1, limit)) { ok = false; break; }
+      const int cur = __shfl_sync(kFull, nxt, 0);
+      int4 ia = make_int4(-1, 0, 0, 0), ib = make_int4(0, 0, 0, 0);
+      if (cur < n_items) {
+        if (lane == 0) nxt = atomicAdd(&st->ticket, 1);  // its latency hides behind this item's checks
+        ia = __ldg(P.items + 2 * (size_t)(P.item_begin + cur));
+        ib = __ldg(P.items + 2 * (size_t)(P.item_begin + cur) + 1);
+        if (ib.x > 0) {
+          const bool w = ia.x == 5 ? wait_for(&st->prod_wm, P.prod_done, ib.x, P.epoch, st, limit, lane)
+                                   : wait_for(&st->cons_wm, P.cons_done, ib.x, P.epoch, st, limit, lane);
+          if (!w) ia.x = -1;
+        }
+      }
+      if (lane == 0) {
+        volatile int *d = sh.desc[slot];
+        d[0] = ia.x; d[1] = ia.y; d[2] = ia.z; d[3] = ia.w;  // kind, flag index, tile, rows of the tile
+        d[4] = ib.y; d[5] = ib.z; d[6] = ib.w;               // staged rows, their offset, offset of the rows
+        mbar_arrive(&sh.desc_bar[slot]);
+      }
+      __syncwarp();
+      if (ia.x < 0) break;
+    }
+    if (!ok) atomicExch(&st->error, 1);
+  } else if (tid >= kPipeCompute) {
+    // ------------------------------------------------------------------ staging warps
+    const int ptid = tid - kPipeCompute;
+    const int g8 = ptid >> 3, l8 = ptid & 7;
+    unsigned g = 0;  // chunk sequence number of this CTA
+    bool ok = true;
+    for (int t = 0; ok; ++t) {
+      const int slot = t & (kPipeDepth - 1);
+      volatile int *d = sh.desc[slot];
+      if (!warp_wait(&sh.desc_bar[slot], (t / kPipeDepth) & 1, limit)) { ok = false; break; }
+      const int kind = d[0], nH = d[4], hp = d[5];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.desc_free[slot]);
+      if (kind < 0) break;
+      // The control warp acquired (gpu scope) the flags of the tiles this one reads before it posted the
+      // descriptor; the descriptor barrier (release / acquire within the CTA) carries that order over to
+      // this thread's copies, which read T from L2.
+      const TileArrays &ta = kind == 4 ? P.pt : P.ct;
+      const float *src = kind == 4 ? P.in0 : P.inter;
+      // the tile's source row ids, fetched in one batch: lane l of a slot group holds the ids of the
+      // group's steps l, l + 8, ... (step i covers slot g8 + 16 i)
+      int hid[kPipeIdRegs];
+#pragma unroll
+      for (int u = 0; u < kPipeIdRegs; ++u) {
+        const int s = g8 + 16 * (u * 8 + l8);
+        hid[u] = s < nH ? __ldg(ta.halo + hp + s) : 0;
+      }
+      for (int c = 0; c < nchunks; ++c, ++g) {
+        const int buf = g & 1;
+        if (!warp_wait(&sh.empty[buf], ((g >> 1) & 1) ^ 1, limit)) { ok = false; break; }
+        const int c0 = c * 32 + l8 * 4;
+        char *dst = reinterpret_cast<char *>(stage) + (size_t)buf * buf_bytes + l8 * 16;
+        const float *s0 = src + c0;
+        const bool live = c0 < P.n_cols && !(P.debug_flags & 2);
+#pragma unroll
+        for (int u = 0; u < kPipeIdRegs; ++u) {
+          if (128 * u >= nH) break;  // uniform over the CTA
+#pragma unroll
+          for (int l = 0; l < 8; ++l) {
+            const int s = g8 + 16 * (u * 8 + l);
+            const int r = __shfl_sync(kFull, hid[u], l, 8);
+            if (live && s < nH) cp_async16(dst + s * 128, s0 + (size_t)r * P.n_cols);
+          }
+        }
+        cp_async_arrive(&sh.full[buf]);
+      }
+    }
+    if (!ok) atomicExch(&st->error, 1);
+  } else {
+    // ------------------------------------------------------------------ compute warps
+    const int g4 = tid >> 2, l4 = tid & 3;
+    const int colA = ((g4 & 1) * 16) + l4 * 4, colB = (((g4 & 1) ^ 1) * 16) + l4 * 4;  // floats within the chunk
+    unsigned g = 0;
+    bool ok = true;
+    for (int t = 0; ok; ++t) {
+      const int slot = t & (kPipeDepth - 1);
+      volatile int *d = sh.desc[slot];
+      if (!warp_wait(&sh.desc_bar[slot], (t / kPipeDepth) & 1, limit)) { ok = false; break; }
+      const int kind = d[0], block = d[1], nR = d[3], rp = d[6];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.desc_free[slot]);
+      if (kind < 0) break;
+      const bool first = kind == 4;
+      const TileArrays &ta = first ? P.pt : P.ct;
+      const int *ap = first ? P.f_ap : P.s_ap;
+      const float *ax = first ? P.f_ax : P.s_ax;
+      float *dst = first ? P.inter : P.out;
+      const bool relu = !first && P.relu != 0;
+      // rows of this lane group; lane l holds the (slot, value) pairs l and l + 4 of each row
+      int rr[kTileRowsPerGroup], cnt[kTileRowsPerGroup], ms[kTileRowsPerGroup][2];
+      float mv[kTileRowsPerGroup][2];
+      int wmax = 0;
+#pragma unroll
+      for (int j = 0; j < kTileRowsPerGroup; ++j) {
+        const int i = j * kPipeGroups + g4;
+        rr[j] = -1; cnt[j] = 0;
+        ms[j][0] = ms[j][1] = 0; mv[j][0] = mv[j][1] = 0.f;
+        if (i < nR) {
+          const size_t e = (size_t)rp + i;
+          rr[j] = __ldg(ta.rows + e);
+          cnt[j] = __ldg(ta.ecnt + e);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {  // rows shorter than 8 are padded with slot 0, value 0
+            ms[j][h] = (int)__ldg(ta.eslot + e * 8 + l4 + 4 * h) * 128;
+            mv[j][h] = __ldg(ta.eval + e * 8 + l4 + 4 * h);
+          }
+        }
+        wmax = max(wmax, cnt[j]);
+      }
+      wmax = __reduce_max_sync(kFull, wmax);
+      const int kshort = min(wmax, 8);
+      for (int c = 0; c < nchunks; ++c, ++g) {
+        const int buf = g & 1;
+        if (!warp_wait(&sh.full[buf], (g >> 1) & 1, limit)) { ok = false; break; }
+        const char *bA = reinterpret_cast<const char *>(stage) + (size_t)buf * buf_bytes + colA * 4;
+        const char *bB = reinterpret_cast<const char *>(stage) + (size_t)buf * buf_bytes + colB * 4;
+        const int c0 = c * 32;
+#pragma unroll
+        for (int j = 0; j < kTileRowsPerGroup; ++j) {
+          if (j * kPipeGroups + (tid >> 5) * 8 >= nR) continue;  // this warp has no rows in round j
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            if (k < kshort && !(P.debug_flags & 1)) {  // uniform over the warp
+              const int off = __shfl_sync(kFull, ms[j][k >> 2], k & 3, 4);
+              const float v = __shfl_sync(kFull, mv[j][k >> 2], k & 3, 4);
+              const float4 x = *reinterpret_cast<const float4 *>(bA + off);
+              const float4 y = *reinterpret_cast<const float4 *>(bB + off);
+              if (k < cnt[j]) {  // padding names slot 0, whose contents must not reach the sum
+                a.x = fmaf(v, x.x, a.x); a.y = fmaf(v, x.y, a.y); a.z = fmaf(v, x.z, a.z); a.w = fmaf(v, x.w, a.w);
+                b.x = fmaf(v, y.x, b.x); b.y = fmaf(v, y.y, b.y); b.z = fmaf(v, y.z, b.z); b.w = fmaf(v, y.w, b.w);
+              }
+            }
+          }
+          if (wmax > 8) {  // rows with more than 8 nonzeros: the rest comes straight from the CSR arrays
+            const int longest = __reduce_max_sync(kFull, cnt[j]);
+            const int p0 = rr[j] >= 0 ? __ldg(ap + rr[j]) : 0;
+            for (int q = 8; q < longest; q += 4) {
+              int s2 = 0;
+              float v2 = 0.f;
+              if (q + l4 < cnt[j]) { s2 = (int)__ldg(ta.slot + p0 + q + l4) * 128; v2 = __ldg(ax + p0 + q + l4); }
+              for (int k = 0; k < 4; ++k) {
+                const int off = __shfl_sync(kFull, s2, k, 4);
+                const float v = __shfl_sync(kFull, v2, k, 4);
+                const float4 x = *reinterpret_cast<const float4 *>(bA + off);
+                const float4 y = *reinterpret_cast<const float4 *>(bB + off);
+                if (q + k < cnt[j]) {
+                  a.x = fmaf(v, x.x, a.x); a.y = fmaf(v, x.y, a.y); a.z = fmaf(v, x.z, a.z); a.w = fmaf(v, x.w, a.w);
+                  b.x = fmaf(v, y.x, b.x); b.y = fmaf(v, y.y, b.y); b.z = fmaf(v, y.z, b.z); b.w = fmaf(v, y.w, b.w);
+                }
+              }
+            }
+          }
+          if (rr[j] >= 0 && !(P.debug_flags & 4)) {
+            if (relu) {
+              a.x = fmaxf(a.x, 0.f); a.y = fmaxf(a.y, 0.f); a.z = fmaxf(a.z, 0.f); a.w = fmaxf(a.w, 0.f);
+              b.x = fmaxf(b.x, 0.f); b.y = fmaxf(b.y, 0.f); b.z = fmaxf(b.z, 0.f); b.w = fmaxf(b.w, 0.f);
+            }
+            float *o = dst + (size_t)rr[j] * P.n_cols + c0;
+            if (c0 + colA < P.n_cols) *reinterpret_cast<float4 *>(o + colA) = a;
+            if (c0 + colB < P.n_cols) *reinterpret_cast<float4 *>(o + colB) = b;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.empty[buf]);
+      }
+      if (!ok) break;
+      if (first) {
+        // the last compute warp to finish the tile publishes it
+        __syncwarp();
+        if (lane == 0) {
+          // orders this warp's stores before the count within the CTA; the warp that publishes fences at
+          // gpu scope, which covers everything that happened before its own increment
+          __threadfence_block();
+          int *cntp = &sh.done_cnt[slot];
+          if (atomicAdd(cntp, 1) == kPipeCompute / 32 - 1) {
+            *cntp = 0;
+            publish(P.prod_done, block, P.epoch);
+          }
+        }
+      }
+    }
+    if (!ok) atomicExch(&st->error, 1);
+  }
+  // the last CTA out rewinds the ticket counter (and, after the last phase, the watermarks)
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const int f = atomicAdd(&st->finished, 1);
+    if (f == (int)gridDim.x - 1) {
+      st->ticket = 0;
+      st->finished = 0;
+      if (P.reset_wm) { st->prod_wm = 0; st->cons_wm = 0; }
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace
+
+// shared memory the pipeline needs for tiles of up to tile_slots staged rows; 0 when it cannot run them
+size_t tile_pipeline_smem(int tile_slots) {
+  return tile_slots > 0 && tile_slots <= kPipeMaxSlots ? (size_t)2 * tile_slots * 128 : 0;
+}
+
+cudaError_t launch_tile_pipeline(int grid, int tile_slots, const Params &p, cudaStream_t s) {
+  const size_t dyn = tile_pipeline_smem(tile_slots);
+  cudaError_t e = cudaFuncSetAttribute((const void *)tile_pipeline_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+  if (e != cudaSuccess) return e;
+  if (p.debug_flags & 8) { const int ns = 64; cudaMemcpyToSymbolAsync(g_pipe_sleep, &ns, sizeof(int), 0, cudaMemcpyHostToDevice, s); }
+  tile_pipeline_kernel<<<grid, kPipeThreads, dyn, s>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace tfk
