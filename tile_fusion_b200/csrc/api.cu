@@ -77,26 +77,41 @@ struct tf_plan {
   // gather tiles (stream / unfused mode)
   struct DevTiling {
     DevBuf<int> row_ptr, rows, halo_ptr, halo;
-    DevBuf<unsigned short> slot, eslot;
-    DevBuf<int> ecnt;
-    DevBuf<float> eval;
+    DevBuf<unsigned short> slot;
+    DevBuf<int2> meta;
+    std::vector<int> meta_off;  // per tile: offset of its row table, in 16-byte units
     bool on = false;
-    // ap, ax: host CSR of the operator the tiling belongs to
-    int upload(const tf::Tiling &t, const int *ap, const float *ax) {
+    // ap, ax: host CSR of the operator the tiling belongs to; with_meta: build the pipeline's row tables
+    int upload(const tf::Tiling &t, const int *ap, const float *ax, bool with_meta) {
       on = t.tiled;
       if (!on) return TF_OK;
-      const size_t nr = t.rows.size();
-      std::vector<int> cnt(nr);
-      std::vector<unsigned short> es(nr * 8, 0);
-      std::vector<float> ev(nr * 8, 0.f);
-      for (size_t e = 0; e < nr; ++e) {
-        const int r = t.rows[e];
-        cnt[e] = ap[r + 1] - ap[r];
-        for (int k = 0; k < std::min(cnt[e], 8); ++k) { es[e * 8 + k] = t.slot[ap[r] + k]; ev[e * 8 + k] = ax[ap[r] + k]; }
+      int rc = TF_OK;
+      if (with_meta) {
+        const int nt = t.tiles();
+        meta_off.assign(nt + 1, 0);
+        size_t pairs = 0;
+        for (int k = 0; k < nt; ++k) {
+          meta_off[k] = (int)(pairs / 2);
+          pairs += (size_t)tfk::kTileMetaPlanes * ((t.tile_row_ptr[k + 1] - t.tile_row_ptr[k] + 7) / 8 * 8);
+        }
+        std::vector<int2> m(pairs, make_int2(0, 0));
+        for (int k = 0; k < nt; ++k) {
+          const int rp = t.tile_row_ptr[k], nR = t.tile_row_ptr[k + 1] - rp, R = (nR + 7) / 8 * 8;
+          int2 *blk = m.data() + 2 * (size_t)meta_off[k];
+          for (int i = 0; i < R; ++i) blk[tfk::kTileMetaNnz * R + i] = make_int2(-1, 0);
+          for (int i = 0; i < nR; ++i) {
+            const int r = t.rows[rp + i], cnt = ap[r + 1] - ap[r];
+            blk[tfk::kTileMetaNnz * R + i] = make_int2(r, cnt);
+            for (int q = 0; q < std::min(cnt, tfk::kTileMetaNnz); ++q) {
+              int2 e;
+              e.x = (int)t.slot[ap[r] + q] * 128;
+              std::memcpy(&e.y, &ax[ap[r] + q], 4);
+              blk[q * R + i] = e;
+            }
+          }
+        }
+        rc = meta.upload(m);
       }
-      int rc = ecnt.upload(cnt);
-      if (rc == TF_OK) rc = eslot.upload(es);
-      if (rc == TF_OK) rc = eval.upload(ev);
       if (rc == TF_OK) rc = row_ptr.upload(t.tile_row_ptr);
       if (rc == TF_OK) rc = rows.upload(t.rows);
       if (rc == TF_OK) rc = halo_ptr.upload(t.tile_halo_ptr);
@@ -105,15 +120,15 @@ struct tf_plan {
       return rc;
     }
     tfk::TileArrays view() const {
-      tfk::TileArrays a{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-      if (on) a = tfk::TileArrays{row_ptr.p, rows.p, halo_ptr.p, halo.p, slot.p, ecnt.p, eslot.p, eval.p};
+      tfk::TileArrays a{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+      if (on) a = tfk::TileArrays{row_ptr.p, rows.p, halo_ptr.p, halo.p, slot.p, meta.p};
       return a;
     }
   } ptile, ctile;
   size_t dyn_smem = 0;
   int tile_slots = 0;
   bool pipe = false;  // every item of phases 1 and 2 is a gather tile: run them on the tile pipeline
-  int pipe_grid = 0;
+  int pipe_grid = 0, pipe_rows = 0;
   // tensor-core dense producer
   bool use_tc = false;
   DevBuf<float> w_hi, w_lo;  // split, transposed weight [n_cols][k]
@@ -163,8 +178,8 @@ int default_rows_per_block(int n_cols, bool gemm) {
 }
 
 // pt, ct: the gather tiles of a plan the tile pipeline runs; its tile items carry the extents of the
-// tile ({kind, flag, tile, rows} {need, staged rows, offset of the staged rows, offset of the rows}),
-// so that the kernel needs no further lookup before it can start on a tile.
+// tile ({kind, flag, tile, rows rounded up to 8} {need, staged rows, offset of the staged rows, offset
+// of the row table}), so that the kernel needs no further lookup before it can start on a tile.
 int upload_items(tf_plan &p, const tf::Tiling *pt = nullptr, const tf::Tiling *ct = nullptr) {
   std::vector<int4> raw(2 * p.hp.items.size());
   for (size_t i = 0; i < p.hp.items.size(); ++i) {
@@ -174,8 +189,9 @@ int upload_items(tf_plan &p, const tf::Tiling *pt = nullptr, const tf::Tiling *c
     if (p.pipe && (it.kind == tf::ITEM_PRODUCE_TILED || it.kind == tf::ITEM_CONSUME_TILED)) {
       const tf::Tiling &t = it.kind == tf::ITEM_PRODUCE_TILED ? *pt : *ct;
       const int k = it.row_begin;
-      raw[2 * i].w = t.tile_row_ptr[k + 1] - t.tile_row_ptr[k];
-      raw[2 * i + 1] = make_int4(it.need, t.tile_halo_ptr[k + 1] - t.tile_halo_ptr[k], t.tile_halo_ptr[k], t.tile_row_ptr[k]);
+      const tf_plan::DevTiling &dt = it.kind == tf::ITEM_PRODUCE_TILED ? p.ptile : p.ctile;
+      raw[2 * i].w = (t.tile_row_ptr[k + 1] - t.tile_row_ptr[k] + 7) / 8 * 8;
+      raw[2 * i + 1] = make_int4(it.need, t.tile_halo_ptr[k + 1] - t.tile_halo_ptr[k], t.tile_halo_ptr[k], dt.meta_off[k]);
     }
   }
   int rc = p.items.upload(raw);
@@ -331,7 +347,34 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
   // a tile holds one row per 4 lanes... of the CTA that runs it: 256 rows (sparse chains) or 512 (GeMM-SpMM)
   const int tile_rows = tfk::tiled_threads(chain);
   const int slots = o.tile_slots == 0 ? (chain == 1 ? tf::kDefaultTileSlots : tf::kDefaultTileSlotsSmall) : o.tile_slots;
-  if (o.mode != TF_MODE_SCHEDULE && slots > 0 && n_cols % 4 == 0) {
+  // SpMM-SpMM with both operators tiled runs on the tile pipeline (one CTA per SM, about four tiles in
+  // flight each).  Its tiles are a little smaller: two chunk buffers and two row tables share the SM's
+  // shared memory.  It has no ring addressing, so a ring is only kept when the caller asked for one.
+  bool want_pipe = false;
+  {
+    const int ps = o.tile_slots == 0 ? tf::kPipeTileSlots : o.tile_slots;
+    const size_t need = tfk::tile_pipeline_smem(ps, tf::kPipeTileRows);
+    if (chain == 0 && F && o.mode != TF_MODE_SCHEDULE && o.tile_pipeline >= 0 && o.ring_bytes <= 0 &&
+        o.tile_double_buffer <= 0 && n_cols % 4 == 0 && need > 0 && need <= 226 * 1024) {
+      const int max_bz = o.tile_max_bz > 0 ? o.tile_max_bz : tf::kDefaultTileMaxBz;
+      tf::build_tiling(F->m, F->ap, F->ai, ps, max_bz, tf::kPipeTileRows, pt);
+      tf::build_tiling(A->m, A->ap, A->ai, ps, max_bz, tf::kPipeTileRows, ct);
+      if (pt.tiled && ct.tiled) {
+        want_pipe = true;
+        p->tile_slots = ps;
+        p->pipe_rows = tf::kPipeTileRows;
+        p->dyn_smem = (size_t)ps * 132;  // for the launches of phase 0, which run on the two-CTA kernel
+        rc = finish_plan(*p, o, sm_count, false);
+        if (rc != TF_OK) return rc;
+        pp.ring_bytes = -1;
+        pp.max_ctas = 4 * sm_count;
+      } else {
+        pt = tf::Tiling();
+        ct = tf::Tiling();
+      }
+    }
+  }
+  if (!want_pipe && o.mode != TF_MODE_SCHEDULE && slots > 0 && n_cols % 4 == 0) {
     const int max_bz = o.tile_max_bz > 0 ? o.tile_max_bz : tf::kDefaultTileMaxBz;
     const bool dbl = o.tile_double_buffer > 0 || (o.tile_double_buffer == 0 && tf::kDefaultTileDoubleBuffer);
     const int cap = dbl ? slots / 2 : slots;  // half-size tiles leave room for the next chunk's copies
@@ -360,17 +403,12 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
     if (rc != TF_OK) return rc;
     pp.max_ctas = p->grid;
   }
-  // both operators tiled: the tile pipeline runs the chain (one CTA per SM, about three tiles in flight
-  // each); it has no ring addressing, so a ring is only kept when the caller asked for one
-  const bool want_pipe = chain == 0 && pt.tiled && ct.tiled && o.tile_pipeline >= 0 && o.ring_bytes <= 0 &&
-                         tfk::tile_pipeline_smem(p->tile_slots) > 0 && tfk::tile_pipeline_smem(p->tile_slots) <= 225 * 1024;
-  if (want_pipe) { pp.ring_bytes = -1; pp.max_ctas = 4 * sm_count; }
   p->tile_info[0] = pt.bx; p->tile_info[1] = pt.by; p->tile_info[2] = pt.bz; p->tile_info[3] = pt.tiles();
   p->tile_info[4] = ct.bx; p->tile_info[5] = ct.by; p->tile_info[6] = ct.bz; p->tile_info[7] = ct.tiles();
   rc = tf::build_stream_plan(pp, F ? F->ap : nullptr, F ? F->ai : nullptr, A->ap, A->ai, &pt, &ct, p->hp);
   if (rc != TF_OK) return rc;
-  rc = p->ptile.upload(pt, F ? F->ap : nullptr, F ? F->ax : nullptr);
-  if (rc == TF_OK) rc = p->ctile.upload(ct, A->ap, A->ax);
+  rc = p->ptile.upload(pt, F ? F->ap : nullptr, F ? F->ax : nullptr, want_pipe);
+  if (rc == TF_OK) rc = p->ctile.upload(ct, A->ap, A->ax, want_pipe);
   if (rc != TF_OK) return rc;
   p->pipe = want_pipe && p->hp.ring_rows == 0;
   for (int i = p->hp.phase_begin[1]; p->pipe && i < p->hp.phase_begin[3]; ++i)
@@ -431,6 +469,7 @@ tfk::Params base_params(tf_plan &p) {
   P.ring_rows = (int)p.hp.ring_rows;
   P.n_prod = p.hp.n_prod;
   P.n_cons = p.hp.n_cons;
+  P.tile_rows = p.pipe_rows;
   P.pt = p.ptile.view();
   P.ct = p.ctile.view();
   P.tile_slots = p.tile_slots;
@@ -469,7 +508,7 @@ int prepare_tc(tf_plan &p, tfk::Params &P, cudaStream_t s) {
 
 // One launch over the items [Q.item_begin, Q.item_end) of phases 1 and 2.
 cudaError_t launch_items(tf_plan &p, int vec, int ch, bool ring, const tfk::Params &Q, cudaStream_t s) {
-  if (p.pipe) return tfk::launch_tile_pipeline(p.pipe_grid, p.tile_slots, Q, s);
+  if (p.pipe) return tfk::launch_tile_pipeline(p.pipe_grid, Q, s);
   return tfk::launch_stream(p.chain, vec, ch, ring, p.grid, p.dyn_smem, Q, s);
 }
 

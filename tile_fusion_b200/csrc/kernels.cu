@@ -92,15 +92,80 @@ __device__ __forceinline__ void gemm_rows_cta(const float *__restrict__ B, const
 // ---------------------------------------------------------------------------
 // SDDMM-SpMM row: D[row] = sum_p (ax[p] * <Q[row], K[col_p]>) * V[col_p]
 // ---------------------------------------------------------------------------
+// acc += sum over the nonzeros [q0, q1) of one row of ax[p] * <Q[row], K[col_p]> * V[col_p, panel columns].
+// Eight nonzeros at a time: their K rows are read together (lane t holds the products of columns t,
+// t + 32, ...), the eight partial dot products are reduced across the warp in one transposed pass (nine
+// shuffles instead of forty), and the eight V rows are then gathered together.
+template <int VEC, int CH>
+__device__ __forceinline__ void sddmm_accumulate(const Params &P, const float *__restrict__ qrow, int q0, int q1,
+                                                 int col0, float (&acc)[CH][VEC], int lane) {
+  const int kq = P.k_dim, nv = P.n_cols;
+  const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+  for (int p = q0; p < q1; p += 32) {
+    const int cnt = min(32, q1 - p);
+    int col = 0;
+    float val = 0.f;
+    if (lane < cnt) { col = __ldg(P.s_ai + p + lane); val = __ldg(P.s_ax + p + lane); }
+    for (int k0 = 0; k0 < cnt; k0 += 8) {
+      const float *krow[8];
+      int cu[8];
+      float part[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {  // lanes past the end name column 0 with value 0; their sums are dropped
+        cu[u] = __shfl_sync(kFull, col, k0 + u);
+        krow[u] = P.in1 + (size_t)cu[u] * kq;
+        part[u] = 0.f;
+      }
+      for (int t = lane; t < kq; t += 32) {
+        const float qv = __ldg(qrow + t);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) part[u] = fmaf(qv, __ldg(krow[u] + t), part[u]);
+      }
+      // transposed reduction: afterwards the four lanes 4u .. 4u + 3 hold the dot product of nonzero k0 + u
+      float h4[4], h2[2], dot;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float send = b4 ? part[i] : part[i + 4], keep = b4 ? part[i + 4] : part[i];
+        h4[i] = keep + __shfl_xor_sync(kFull, send, 16);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float send = b3 ? h4[i] : h4[i + 2], keep = b3 ? h4[i + 2] : h4[i];
+        h2[i] = keep + __shfl_xor_sync(kFull, send, 8);
+      }
+      {
+        const float send = b2 ? h2[0] : h2[1], keep = b2 ? h2[1] : h2[0];
+        dot = keep + __shfl_xor_sync(kFull, send, 4);
+      }
+      dot += __shfl_xor_sync(kFull, dot, 2);
+      dot += __shfl_xor_sync(kFull, dot, 1);
+      const float sc = dot * __shfl_sync(kFull, val, k0 + (lane >> 2));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (k0 + u < cnt) {  // uniform over the warp
+          const float s = __shfl_sync(kFull, sc, 4 * u);
+          const float *vrow = P.in2 + (size_t)cu[u] * nv + col0;
+#pragma unroll
+          for (int ch = 0; ch < CH; ++ch) {
+            const int cc = (ch * 32 + lane) * VEC;
+            if (col0 + cc < nv) {
+              float x[VEC];
+              load_vec<VEC, false>(x, vrow + cc);
+#pragma unroll
+              for (int i = 0; i < VEC; ++i) acc[ch][i] = fmaf(s, x[i], acc[ch][i]);
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int VEC, int CH>
 __device__ __forceinline__ void sddmm_row_warp(const Params &P, int row, int lane) {
   const int kq = P.k_dim, nv = P.n_cols;
   const int p0 = __ldg(P.s_ap + row), p1 = __ldg(P.s_ap + row + 1);
-  constexpr int QC = 4;  // Q values kept in registers: kq <= 128
-  float q[QC];
   const float *qrow = P.in0 + (size_t)row * kq;
-#pragma unroll
-  for (int u = 0; u < QC; ++u) q[u] = (lane + 32 * u < kq) ? __ldg(qrow + lane + 32 * u) : 0.f;
   constexpr int PANEL = 32 * VEC * CH;
   for (int col0 = 0; col0 < nv; col0 += PANEL) {
     float acc[CH][VEC];
@@ -108,36 +173,7 @@ __device__ __forceinline__ void sddmm_row_warp(const Params &P, int row, int lan
     for (int c = 0; c < CH; ++c)
 #pragma unroll
       for (int i = 0; i < VEC; ++i) acc[c][i] = 0.f;
-    for (int p = p0; p < p1; p += 32) {
-      const int cnt = min(32, p1 - p);
-      int col = 0;
-      float val = 0.f;
-      if (lane < cnt) { col = __ldg(P.s_ai + p + lane); val = __ldg(P.s_ax + p + lane); }
-      for (int k = 0; k < cnt; ++k) {
-        const int c = __shfl_sync(kFull, col, k);
-        const float a = __shfl_sync(kFull, val, k);
-        const float *krow = P.in1 + (size_t)c * kq;
-        float part = 0.f;
-#pragma unroll
-        for (int u = 0; u < QC; ++u)
-          if (lane + 32 * u < kq) part = fmaf(q[u], __ldg(krow + lane + 32 * u), part);
-        for (int t = lane + 32 * QC; t < kq; t += 32) part = fmaf(__ldg(qrow + t), __ldg(krow + t), part);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(kFull, part, o);
-        const float s = part * a;
-        const float *vrow = P.in2 + (size_t)c * nv + col0;
-#pragma unroll
-        for (int ch = 0; ch < CH; ++ch) {
-          const int cc = (ch * 32 + lane) * VEC;
-          if (col0 + cc < nv) {
-            float x[VEC];
-            load_vec<VEC, false>(x, vrow + cc);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) acc[ch][i] = fmaf(s, x[i], acc[ch][i]);
-          }
-        }
-      }
-    }
+    sddmm_accumulate<VEC, CH>(P, qrow, p0, p1, col0, acc, lane);
     float *orow = P.out + (size_t)row * nv;
 #pragma unroll
     for (int ch = 0; ch < CH; ++ch) {
@@ -165,33 +201,7 @@ __device__ __forceinline__ void sddmm_range_cta(const Params &P, int row, int p0
     for (int c = 0; c < CH; ++c)
 #pragma unroll
       for (int i = 0; i < VEC; ++i) acc[c][i] = 0.f;
-    for (int p = q0; p < q1; p += 32) {
-      const int cnt = min(32, q1 - p);
-      int col = 0;
-      float val = 0.f;
-      if (lane < cnt) { col = __ldg(P.s_ai + p + lane); val = __ldg(P.s_ax + p + lane); }
-      for (int k = 0; k < cnt; ++k) {
-        const int c = __shfl_sync(kFull, col, k);
-        const float a = __shfl_sync(kFull, val, k);
-        const float *krow = P.in1 + (size_t)c * kq;
-        float part = 0.f;
-        for (int t = lane; t < kq; t += 32) part = fmaf(__ldg(qrow + t), __ldg(krow + t), part);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(kFull, part, o);
-        const float s = part * a;
-        const float *vrow = P.in2 + (size_t)c * nv + col0;
-#pragma unroll
-        for (int ch = 0; ch < CH; ++ch) {
-          const int cc = (ch * 32 + lane) * VEC;
-          if (col0 + cc < nv) {
-            float x[VEC];
-            load_vec<VEC, false>(x, vrow + cc);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) acc[ch][i] = fmaf(s, x[i], acc[ch][i]);
-          }
-        }
-      }
-    }
+    sddmm_accumulate<VEC, CH>(P, qrow, q0, q1, col0, acc, lane);
 #pragma unroll
     for (int c = 0; c < CH; ++c)
 #pragma unroll
@@ -226,7 +236,7 @@ union StreamSmem {
 // TILED: the plan holds gather tiles (item kinds 4 and 5); their staging buffer allows two CTAs per
 // SM, so that variant may use twice the registers.
 template <int MODE, int VEC, int CH, bool RING, bool TILED>
-__global__ void __launch_bounds__(TILED ? tiled_threads(MODE) : kThreads, TILED ? 2 : TF_MIN_CTAS)
+__global__ void __launch_bounds__(TILED ? tiled_threads(MODE) : kThreads, TILED ? 2 : (MODE == 2 ? 3 : TF_MIN_CTAS))
     stream_kernel(const __grid_constant__ Params P) {
   constexpr int NT = TILED ? tiled_threads(MODE) : kThreads;
   constexpr int NW = NT / 32;

@@ -36,12 +36,13 @@ struct ExecState {
 struct TileArrays {
   const int *row_ptr, *rows, *halo_ptr, *halo;
   const unsigned short *slot;
-  // in tile-row order (index row_ptr[tile] + i): the row's length and its first 8 (slot, value) pairs,
-  // padded with slot 0 / value 0
-  const int *ecnt;
-  const unsigned short *eslot;
-  const float *eval;
+  // Row tables for the tile pipeline, one block per tile of kTileMetaPlanes planes of R pairs (R = the
+  // tile's rows rounded up to 8): plane k < kTileMetaNnz holds {byte offset of the slot, value bits} of
+  // nonzero k of every row ({0, 0} past the row's end), the last plane {row id or -1, row length}.
+  const int2 *meta;
 };
+constexpr int kTileMetaNnz = 7;
+constexpr int kTileMetaPlanes = kTileMetaNnz + 1;
 
 struct Params {
   // first operator (SpMM producer) and second operator (consumer), device CSR
@@ -71,6 +72,7 @@ struct Params {
   int debug_flags;   // diagnostics only: 1 = skip the tile compute loop, 2 = skip the tile staging copies
   TileArrays pt, ct; // gather tiles of the first / second operator (null when not tiled)
   int tile_slots;    // staging slots per CTA (dynamic shared memory holds tile_slots * 132 bytes)
+  int tile_rows;     // tile pipeline: most rows of a tile, rounded up to 8
 };
 
 // ---------------------------------------------------------------------------

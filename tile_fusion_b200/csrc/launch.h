@@ -19,8 +19,8 @@ cudaError_t launch_schedule_level(int mode, int vec, int ch, int grid, const Par
 cudaError_t launch_spmm(int vec, int ch, int grid, const int *ap, const int *ai, const float *ax, int m,
                         const float *x, int n_cols, float *out, cudaStream_t s);
 // gather-tile pipeline (one CTA per SM): plans whose items are all gather tiles
-size_t tile_pipeline_smem(int tile_slots);
-cudaError_t launch_tile_pipeline(int grid, int tile_slots, const Params &p, cudaStream_t s);
+size_t tile_pipeline_smem(int tile_slots, int tile_rows);
+cudaError_t launch_tile_pipeline(int grid, const Params &p, cudaStream_t s);
 cudaError_t launch_rows_fix(const int *rows, int n_rows, int n_cols, float *x, bool relu, cudaStream_t s);
 cudaError_t launch_fill(bool normal, float *p, long long n, unsigned long long seed, long long off, float sigma,
                         cudaStream_t s);

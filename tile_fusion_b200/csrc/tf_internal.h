@@ -17,6 +17,9 @@ namespace tf {
 
 constexpr int kDefaultTileSlots = 800;  // 100 KB of staging per CTA: two CTAs per SM
 constexpr int kDefaultTileSlotsSmall = kDefaultTileSlots;
+// tile pipeline: 3 x 512 x 128 B of chunk buffers + 2 x 8 x 256 x 8 B of row tables = 229 376 B per SM
+constexpr int kPipeTileSlots = 512;
+constexpr int kPipeTileRows = 256;
 constexpr int kDefaultTileMaxBz = 8;
 constexpr int kHeavyRowNnz = 512;    // a row at least this long is a block of its own (the CTA's warps share it)
 constexpr int kSegmentNnz = 4096;    // a row longer than this is cut into segments run by different CTAs

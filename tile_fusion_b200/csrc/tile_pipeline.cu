@@ -4,11 +4,15 @@
 // producer tiles an item depends on and posts a tile descriptor, up to four tiles ahead of the
 // others, so the latency of the ticket, the item record and the flag checks stays off the data
 // path.  Four staging warps copy the tile's source rows -- one 32-column chunk (128 bytes per row)
-// at a time -- into one of two shared-memory buffers with 16-byte asynchronous copies whose
+// at a time -- into one of three shared-memory buffers with 16-byte asynchronous copies whose
 // completion is counted by an mbarrier.  Sixteen compute warps wait for a full
 // buffer, form the tile's output rows for that chunk from shared memory, store them, and hand
 // the buffer back.  Copies for chunk g + 1 (of this or of the next tile) are therefore in
 // flight while chunk g is computed, and neither side ever meets the other at a CTA barrier.
+//
+// The tile's row table travels with its first chunk: eight planes of R (offset, value) pairs -- plane k < 7
+// holds nonzero k of every row, the eighth the row id and length -- so that the eight rows a warp works
+// on read one contiguous 64-byte line per nonzero and keep nothing about the tile in registers.
 //
 // Every wait is bounded: a wait that runs out sets the sticky error flag of the launch and the
 // thread leaves its loop; the others then run out of their own waits and follow.
@@ -23,18 +27,21 @@ namespace {
 constexpr int kPipeCompute = 512;  // 16 compute warps: 4 lanes per row, up to 4 rows per lane group
 constexpr int kPipeStagers = 128;  // 4 staging warps: 8 lanes per 128-byte slot, 16 slots per step
 constexpr int kPipeThreads = kPipeCompute + kPipeStagers + 32;  // + the control warp
+constexpr int kPipeStages = 3;     // chunk buffers: two fills are in flight while one chunk is computed
 constexpr int kPipeDepth = 4;      // tile descriptors in flight
 constexpr int kPipeReaders = (kPipeCompute + kPipeStagers) / 32;  // warps that read every descriptor
 constexpr int kPipeGroups = kPipeCompute / 4;
-constexpr int kPipeIdRegs = 7;     // source row ids per staging lane: 7 * 8 steps * 16 slot groups = 896 slots
+constexpr int kPipeRounds = 3;     // rows per lane group: a tile holds at most 3 * 128 rows
+constexpr int kPipeIdRegs = 4;     // source row ids per staging lane: 4 * 8 steps * 16 slot groups = 512 slots
 constexpr int kPipeMaxSlots = kPipeIdRegs * 8 * 16;
 
 struct PipeShared {
-  unsigned long long full[2];            // a chunk buffer holds its copies (one arrival per staging thread)
-  unsigned long long empty[2];           // its readers are done (one arrival per compute warp)
+  unsigned long long full[kPipeStages];          // a chunk buffer holds its copies (one arrival per staging thread)
+  unsigned long long empty[kPipeStages];          // its readers are done (one arrival per compute warp)
   unsigned long long desc_bar[kPipeDepth];   // descriptor posted (control warp)
   unsigned long long desc_free[kPipeDepth];  // every reader warp has copied it
-  int desc[kPipeDepth][8];               // kind (-1: no more work), flag index, tile, nR, nH, hp, rp, -
+  int desc[kPipeDepth][8];               // kind (-1: no more work), flag index, tile, rows (rounded up to 8),
+                                         // staged rows, their offset in the halo list, offset of the row table
   int done_cnt[kPipeDepth];              // compute warps that finished the tile
 };
 
@@ -42,16 +49,8 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // bounded wait with a warp-uniform answer (the callers run warp collectives afterwards)
-__device__ int g_pipe_sleep = 0;  // diagnostics: back off between polls
 __device__ __forceinline__ bool warp_wait(unsigned long long *bar, unsigned parity, int limit) {
-  const int ns = g_pipe_sleep;
-  if (ns == 0) return __all_sync(kFull, mbar_wait(bar, parity, limit));
-  bool done = false;
-  for (int i = 0; i < limit && !done; ++i) {
-    done = mbar_wait(bar, parity, 1);
-    if (!done) __nanosleep(ns);
-  }
-  return __all_sync(kFull, done);
+  return __all_sync(kFull, mbar_wait(bar, parity, limit));
 }
 // arrives once every asynchronous copy this thread issued so far has landed
 __device__ __forceinline__ void cp_async_arrive(unsigned long long *bar) {
@@ -59,16 +58,18 @@ __device__ __forceinline__ void cp_async_arrive(unsigned long long *bar) {
 }
 
 __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __grid_constant__ Params P) {
-  extern __shared__ float4 stage[];  // two buffers of tile_slots * 128 bytes
+  extern __shared__ float4 stage[];  // kPipeStages chunk buffers of tile_slots * 128 bytes, two row tables of 9 * tile_rows pairs
   __shared__ PipeShared sh;
   const int tid = threadIdx.x, lane = tid & 31;
   ExecState *st = P.st;
   const int n_items = P.item_end - P.item_begin;
   const int nchunks = (P.n_cols + 31) / 32;
   const int buf_bytes = P.tile_slots * 128;
+  const int meta_bytes = kTileMetaPlanes * P.tile_rows * 8;
+  char *meta_base = reinterpret_cast<char *>(stage) + kPipeStages * (size_t)buf_bytes;
   const int limit = P.spin_limit;
   if (tid == 0) {
-    for (int b = 0; b < 2; ++b) { mbar_init(&sh.full[b], kPipeStagers); mbar_init(&sh.empty[b], kPipeCompute / 32); }
+    for (int b = 0; b < kPipeStages; ++b) { mbar_init(&sh.full[b], kPipeStagers); mbar_init(&sh.empty[b], kPipeCompute / 32); }
     for (int i = 0; i < kPipeDepth; ++i) {
       mbar_init(&sh.desc_bar[i], 1);
       mbar_init(&sh.desc_free[i], kPipeReaders);
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
         if (lane == 0) nxt = atomicAdd(&st->ticket, 1);  // its latency hides behind this item's checks
         ia = __ldg(P.items + 2 * (size_t)(P.item_begin + cur));
         ib = __ldg(P.items + 2 * (size_t)(P.item_begin + cur) + 1);
-        if (ib.x > 0) {
+        if (ib.x > 0 && !(P.debug_flags & 16)) {  // diagnostics: 16 = ignore dependences (wrong results)
           const bool w = ia.x == 5 ? wait_for(&st->prod_wm, P.prod_done, ib.x, P.epoch, st, limit, lane)
                                    : wait_for(&st->cons_wm, P.cons_done, ib.x, P.epoch, st, limit, lane);
           if (!w) ia.x = -1;
@@ -100,8 +101,8 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
       }
       if (lane == 0) {
         volatile int *d = sh.desc[slot];
-        d[0] = ia.x; d[1] = ia.y; d[2] = ia.z; d[3] = ia.w;  // kind, flag index, tile, rows of the tile
-        d[4] = ib.y; d[5] = ib.z; d[6] = ib.w;               // staged rows, their offset, offset of the rows
+        d[0] = ia.x; d[1] = ia.y; d[2] = ia.z; d[3] = ia.w;
+        d[4] = ib.y; d[5] = ib.z; d[6] = ib.w;
         mbar_arrive(&sh.desc_bar[slot]);
       }
       __syncwarp();
@@ -118,7 +119,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
       const int slot = t & (kPipeDepth - 1);
       volatile int *d = sh.desc[slot];
       if (!warp_wait(&sh.desc_bar[slot], (t / kPipeDepth) & 1, limit)) { ok = false; break; }
-      const int kind = d[0], nH = d[4], hp = d[5];
+      const int kind = d[0], nRt = d[3], nH = d[4], hp = d[5], moff = d[6];
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh.desc_free[slot]);
       if (kind < 0) break;
@@ -133,11 +134,11 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
 #pragma unroll
       for (int u = 0; u < kPipeIdRegs; ++u) {
         const int s = g8 + 16 * (u * 8 + l8);
-        hid[u] = s < nH ? __ldg(ta.halo + hp + s) : 0;
+        hid[u] = s < nH ? ((P.debug_flags & 32) ? s : __ldg(ta.halo + hp + s)) : 0;  // diagnostics: 32 = no id loads
       }
       for (int c = 0; c < nchunks; ++c, ++g) {
-        const int buf = g & 1;
-        if (!warp_wait(&sh.empty[buf], ((g >> 1) & 1) ^ 1, limit)) { ok = false; break; }
+        const int buf = g % kPipeStages;
+        if (!warp_wait(&sh.empty[buf], ((g / kPipeStages) & 1) ^ 1, limit)) { ok = false; break; }
         const int c0 = c * 32 + l8 * 4;
         char *dst = reinterpret_cast<char *>(stage) + (size_t)buf * buf_bytes + l8 * 16;
         const float *s0 = src + c0;
@@ -151,6 +152,17 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
             const int r = __shfl_sync(kFull, hid[u], l, 8);
             if (live && s < nH) cp_async16(dst + s * 128, s0 + (size_t)r * P.n_cols);
           }
+        }
+        if (c == 0) {  // the tile's row table (16-byte pieces, contiguous in global memory)
+          // Its buffer served tile t - 2, whose last chunk is nchunks + 1 chunks back.  The wait above covers
+          // the chunks up to g - kPipeStages; a closer one (single-chunk tiles) is waited for here.
+          const unsigned gl = g - nchunks - 1;
+          if (t >= 2 && nchunks + 1 < kPipeStages &&
+              !warp_wait(&sh.empty[gl % kPipeStages], (gl / kPipeStages) & 1, limit)) { ok = false; break; }
+          const int4 *msrc = reinterpret_cast<const int4 *>(ta.meta) + moff;
+          char *mdst = meta_base + (size_t)(t & 1) * meta_bytes;
+          const int n16 = kTileMetaPlanes * nRt / 2;
+          for (int q = ptid; q < n16; q += kPipeStagers) cp_async16(mdst + q * 16, msrc + q);
         }
         cp_async_arrive(&sh.full[buf]);
       }
@@ -166,7 +178,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
       const int slot = t & (kPipeDepth - 1);
       volatile int *d = sh.desc[slot];
       if (!warp_wait(&sh.desc_bar[slot], (t / kPipeDepth) & 1, limit)) { ok = false; break; }
-      const int kind = d[0], block = d[1], nR = d[3], rp = d[6];
+      const int kind = d[0], block = d[1], nRt = d[3];
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh.desc_free[slot]);
       if (kind < 0) break;
@@ -176,77 +188,59 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
       const float *ax = first ? P.f_ax : P.s_ax;
       float *dst = first ? P.inter : P.out;
       const bool relu = !first && P.relu != 0;
-      // rows of this lane group; lane l holds the (slot, value) pairs l and l + 4 of each row
-      int rr[kTileRowsPerGroup], cnt[kTileRowsPerGroup], ms[kTileRowsPerGroup][2];
-      float mv[kTileRowsPerGroup][2];
-      int wmax = 0;
-#pragma unroll
-      for (int j = 0; j < kTileRowsPerGroup; ++j) {
-        const int i = j * kPipeGroups + g4;
-        rr[j] = -1; cnt[j] = 0;
-        ms[j][0] = ms[j][1] = 0; mv[j][0] = mv[j][1] = 0.f;
-        if (i < nR) {
-          const size_t e = (size_t)rp + i;
-          rr[j] = __ldg(ta.rows + e);
-          cnt[j] = __ldg(ta.ecnt + e);
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {  // rows shorter than 8 are padded with slot 0, value 0
-            ms[j][h] = (int)__ldg(ta.eslot + e * 8 + l4 + 4 * h) * 128;
-            mv[j][h] = __ldg(ta.eval + e * 8 + l4 + 4 * h);
-          }
-        }
-        wmax = max(wmax, cnt[j]);
-      }
-      wmax = __reduce_max_sync(kFull, wmax);
-      const int kshort = min(wmax, 8);
+      // row table of this tile: plane k at k * nRt pairs, the row ids and lengths in plane 8
+      const int2 *meta = reinterpret_cast<const int2 *>(meta_base + (size_t)(t & 1) * meta_bytes);
       for (int c = 0; c < nchunks; ++c, ++g) {
-        const int buf = g & 1;
-        if (!warp_wait(&sh.full[buf], (g >> 1) & 1, limit)) { ok = false; break; }
+        const int buf = g % kPipeStages;
+        if (!warp_wait(&sh.full[buf], (g / kPipeStages) & 1, limit)) { ok = false; break; }
         const char *bA = reinterpret_cast<const char *>(stage) + (size_t)buf * buf_bytes + colA * 4;
         const char *bB = reinterpret_cast<const char *>(stage) + (size_t)buf * buf_bytes + colB * 4;
         const int c0 = c * 32;
 #pragma unroll
-        for (int j = 0; j < kTileRowsPerGroup; ++j) {
-          if (j * kPipeGroups + (tid >> 5) * 8 >= nR) continue;  // this warp has no rows in round j
+        for (int j = 0; j < kPipeRounds; ++j) {
+          if (j * kPipeGroups + (tid >> 5) * 8 >= nRt) continue;  // this warp has no rows in round j
+          const int i = j * kPipeGroups + g4;
+          const int2 rc = meta[kTileMetaNnz * nRt + i];  // row id (-1: padding), length
+          const int longest = __reduce_max_sync(kFull, rc.y);
+          const int kmax = min(longest, kTileMetaNnz);
           float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            if (k < kshort && !(P.debug_flags & 1)) {  // uniform over the warp
-              const int off = __shfl_sync(kFull, ms[j][k >> 2], k & 3, 4);
-              const float v = __shfl_sync(kFull, mv[j][k >> 2], k & 3, 4);
-              const float4 x = *reinterpret_cast<const float4 *>(bA + off);
-              const float4 y = *reinterpret_cast<const float4 *>(bB + off);
-              if (k < cnt[j]) {  // padding names slot 0, whose contents must not reach the sum
+          for (int k = 0; k < kTileMetaNnz; ++k) {
+            if (k < kmax && !(P.debug_flags & 1)) {  // uniform over the warp
+              const int2 m = meta[k * nRt + i];       // byte offset of the slot, value bits ({0, 0} past the row's end)
+              const float v = __int_as_float(m.y);
+              const float4 x = *reinterpret_cast<const float4 *>(bA + m.x);
+              const float4 y = *reinterpret_cast<const float4 *>(bB + m.x);
+              if (k < rc.y) {  // padding names slot 0, whose contents must not reach the sum
                 a.x = fmaf(v, x.x, a.x); a.y = fmaf(v, x.y, a.y); a.z = fmaf(v, x.z, a.z); a.w = fmaf(v, x.w, a.w);
                 b.x = fmaf(v, y.x, b.x); b.y = fmaf(v, y.y, b.y); b.z = fmaf(v, y.z, b.z); b.w = fmaf(v, y.w, b.w);
               }
             }
           }
-          if (wmax > 8) {  // rows with more than 8 nonzeros: the rest comes straight from the CSR arrays
-            const int longest = __reduce_max_sync(kFull, cnt[j]);
-            const int p0 = rr[j] >= 0 ? __ldg(ap + rr[j]) : 0;
-            for (int q = 8; q < longest; q += 4) {
+          if (longest > kTileMetaNnz) {  // longer rows: the rest comes straight from the CSR arrays
+            const int p0 = rc.x >= 0 ? __ldg(ap + rc.x) : 0;
+            for (int q = kTileMetaNnz; q < longest; q += 4) {
               int s2 = 0;
               float v2 = 0.f;
-              if (q + l4 < cnt[j]) { s2 = (int)__ldg(ta.slot + p0 + q + l4) * 128; v2 = __ldg(ax + p0 + q + l4); }
+              if (q + l4 < rc.y) { s2 = (int)__ldg(ta.slot + p0 + q + l4) * 128; v2 = __ldg(ax + p0 + q + l4); }
               for (int k = 0; k < 4; ++k) {
                 const int off = __shfl_sync(kFull, s2, k, 4);
                 const float v = __shfl_sync(kFull, v2, k, 4);
                 const float4 x = *reinterpret_cast<const float4 *>(bA + off);
                 const float4 y = *reinterpret_cast<const float4 *>(bB + off);
-                if (q + k < cnt[j]) {
+                if (q + k < rc.y) {
                   a.x = fmaf(v, x.x, a.x); a.y = fmaf(v, x.y, a.y); a.z = fmaf(v, x.z, a.z); a.w = fmaf(v, x.w, a.w);
                   b.x = fmaf(v, y.x, b.x); b.y = fmaf(v, y.y, b.y); b.z = fmaf(v, y.z, b.z); b.w = fmaf(v, y.w, b.w);
                 }
               }
             }
           }
-          if (rr[j] >= 0 && !(P.debug_flags & 4)) {
+          if (rc.x >= 0 && !(P.debug_flags & 4)) {
             if (relu) {
               a.x = fmaxf(a.x, 0.f); a.y = fmaxf(a.y, 0.f); a.z = fmaxf(a.z, 0.f); a.w = fmaxf(a.w, 0.f);
               b.x = fmaxf(b.x, 0.f); b.y = fmaxf(b.y, 0.f); b.z = fmaxf(b.z, 0.f); b.w = fmaxf(b.w, 0.f);
             }
-            float *o = dst + (size_t)rr[j] * P.n_cols + c0;
+            float *o = dst + (size_t)rc.x * P.n_cols + c0;
             if (c0 + colA < P.n_cols) *reinterpret_cast<float4 *>(o + colA) = a;
             if (c0 + colB < P.n_cols) *reinterpret_cast<float4 *>(o + colB) = b;
           }
@@ -288,16 +282,18 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
 
 }  // namespace
 
-// shared memory the pipeline needs for tiles of up to tile_slots staged rows; 0 when it cannot run them
-size_t tile_pipeline_smem(int tile_slots) {
-  return tile_slots > 0 && tile_slots <= kPipeMaxSlots ? (size_t)2 * tile_slots * 128 : 0;
+// shared memory the pipeline needs for tiles of up to tile_slots staged rows and tile_rows rows; 0 when
+// it cannot run them
+size_t tile_pipeline_smem(int tile_slots, int tile_rows) {
+  if (tile_slots <= 0 || tile_slots > kPipeMaxSlots || tile_rows <= 0 || tile_rows > kPipeRounds * kPipeGroups) return 0;
+  return (size_t)kPipeStages * tile_slots * 128 + (size_t)2 * kTileMetaPlanes * tile_rows * 8;
 }
 
-cudaError_t launch_tile_pipeline(int grid, int tile_slots, const Params &p, cudaStream_t s) {
-  const size_t dyn = tile_pipeline_smem(tile_slots);
+cudaError_t launch_tile_pipeline(int grid, const Params &p, cudaStream_t s) {
+  const size_t dyn = tile_pipeline_smem(p.tile_slots, p.tile_rows);
+  if (dyn == 0) return cudaErrorInvalidValue;
   cudaError_t e = cudaFuncSetAttribute((const void *)tile_pipeline_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
   if (e != cudaSuccess) return e;
-  if (p.debug_flags & 8) { const int ns = 64; cudaMemcpyToSymbolAsync(g_pipe_sleep, &ns, sizeof(int), 0, cudaMemcpyHostToDevice, s); }
   tile_pipeline_kernel<<<grid, kPipeThreads, dyn, s>>>(p);
   return cudaGetLastError();
 }
