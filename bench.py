@@ -49,7 +49,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (captured on a quarter-size case and scaled by rows)
-DRAM_TRAFFIC = {"c2": 4 * (746_391_040 + 500_188_672)}
+DRAM_TRAFFIC = {"c2": 4 * (713_756_416 + 496_346_368)}
 
 
 def measured_peak_gbs():
@@ -406,7 +406,8 @@ def main():
     achieved = bytes_local / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": None, "peak_source": f"of {peak_kind}", "algorithmic_bytes_per_launch": bytes_local,
-                "kernel": "stream_kernel (persistent fused executor)", "kernel_ms": kernel_ms,
+                "kernel": ("tile_pipeline_kernel" if plan.info()["threads"] == 672 else "stream_kernel")
+                          + " (persistent fused executor)", "kernel_ms": kernel_ms,
                 "kernel_ms_min": float(np.min(per_step))}
     if world == 1 and not args.dims and args.mode == "stream" and args.workload in DRAM_TRAFFIC:
         roofline["traffic"] = DRAM_TRAFFIC[args.workload]
