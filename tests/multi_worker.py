@@ -1,0 +1,64 @@
+"""One rank of the multi-GPU parity check (launched by tests/test_gpu_multi.py through torch.distributed.run).
+
+Every rank owns a row block of a 3-D Laplacian, runs the partitioned chains with the halo exchange over NCCL
+and compares its rows of D with an fp64 product of the whole chain computed on the host."""
+import os
+import sys
+
+import numpy as np
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), ".."))
+
+from tests import common  # noqa: E402
+from tile_fusion_b200 import distributed, partition, synth  # noqa: E402
+
+
+def main():
+    import scipy.sparse as sp
+    import torch
+    import torch.distributed as dist
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    for dims, n, k in (((24, 20, 10 * world), 128, 64), ((40, 33 * world), 32, 16), ((16, 12, 6 * world), 100, 36)):
+        n_rows = int(np.prod(dims))
+        full = synth.laplacian(dims)
+        A64 = sp.csr_matrix((full[2].astype(np.float64), full[1], full[0]), shape=(n_rows, n_rows))
+        bounds = partition.row_bounds(None, n_rows, world)
+        r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
+        a_rows = synth.laplacian_rows(dims, r0, r1)
+        mine = partition.halo_of(a_rows[1], r0, r1)
+        halos = [None] * world
+        dist.all_gather_object(halos, mine)
+        lay = partition.make_layout(rank, bounds, halos)
+        # SpMM-SpMM
+        c = synth.uniform(3, (n_rows, n)) - 0.5
+        ids, fi = partition.compact_columns(a_rows[1])
+        rc = distributed.RankChain("spmm_spmm", lay, a_rows, n, first_rows=(a_rows[0], fi, a_rows[2], len(ids)), device=dev)
+        c_ext = torch.from_numpy(np.ascontiguousarray(c[ids])).to(dev)
+        d = torch.full((r1 - r0, n), float("nan"), device=dev)
+        for _ in range(2):
+            rc.step(c_ext, None, d, dist=dist)
+            rc.plan.status()
+            want = (A64 @ (A64 @ c.astype(np.float64)))[r0:r1]
+            common.assert_close(d.cpu().numpy(), want, f"rank {rank} SpMM-SpMM {dims}")
+        # GeMM-SpMM
+        b, w = synth.uniform(2, (n_rows, k)) - 0.5, synth.uniform(4, (k, n)) - 0.5
+        rg = distributed.RankChain("gemm_spmm", lay, a_rows, n, k=k, device=dev)
+        bd, wd = torch.from_numpy(np.ascontiguousarray(b[r0:r1])).to(dev), torch.from_numpy(w).to(dev)
+        d.fill_(float("nan"))
+        rg.step(bd, wd, d, dist=dist)
+        rg.plan.status()
+        want = (A64 @ (b.astype(np.float64) @ w.astype(np.float64)))[r0:r1]
+        common.assert_close(d.cpu().numpy(), want, f"rank {rank} GeMM-SpMM {dims}")
+        dist.barrier()
+    if rank == 0:
+        print("multi-GPU parity ok on", world, "ranks")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
