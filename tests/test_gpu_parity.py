@@ -56,7 +56,7 @@ def test_spmm_kernel(torch_cuda, oracle, n_cols):
 
 
 @pytest.mark.parametrize("mat", list(MATS))
-@pytest.mark.parametrize("n_cols", [128, 32, 47])
+@pytest.mark.parametrize("n_cols", [128, 32, 47, 64, 100])
 def test_spmm_spmm_all_modes(torch_cuda, oracle, mat, n_cols):
     torch = torch_cuda
     a = common.matrix(MATS[mat])
@@ -68,6 +68,7 @@ def test_spmm_spmm_all_modes(torch_cuda, oracle, mat, n_cols):
     variants = [("stream_ring", dict(mode=api.MODE_STREAM, rows_per_block=16, slack_blocks=4, ring_bytes=1 << 30,
                                      tile_slots=-1)),
                 ("stream_default", dict(mode=api.MODE_STREAM)),
+                ("stream_two_cta_tiles", dict(mode=api.MODE_STREAM, tile_pipeline=-1)),
                 ("stream_noring", dict(mode=api.MODE_STREAM, ring_bytes=-1, rows_per_block=8, tile_slots=-1)),
                 ("tiled_ring", dict(mode=api.MODE_STREAM, tile_slots=160, tile_max_bz=2, ring_bytes=1 << 30,
                                     slack_blocks=3)),
@@ -83,6 +84,10 @@ def test_spmm_spmm_all_modes(torch_cuda, oracle, mat, n_cols):
         plan.status()
         results[name] = d.cpu().numpy()
         common.assert_close(results[name], want, f"{mat} N={n_cols} {name}")
+        if name == "stream_default" and mat.startswith("lap") and n_cols % 4 == 0:
+            assert plan.info()["threads"] == 672, plan.info()  # both operators tiled: the tile pipeline runs it
+        if name == "stream_two_cta_tiles" and mat.startswith("lap") and n_cols % 4 == 0:
+            assert plan.info()["threads"] == 512, plan.info()
         if name == "stream_ring" and mat.startswith("lap"):
             assert 0 < plan.info()["ring_rows"] < A.M
         if name == "tiled_unfused" and mat.startswith("lap") and n_cols % 4 == 0:

@@ -69,7 +69,8 @@ struct Params {
   // tensor-core dense producer (GeMM-SpMM): TMA descriptors of B and of the split, transposed weight
   alignas(64) CUtensorMap tm_a, tm_whi, tm_wlo;
   int use_tc;
-  int debug_flags;   // diagnostics only: 1 = skip the tile compute loop, 2 = skip the tile staging copies
+  int debug_flags;   // diagnostics only (results invalid): 1 = skip the tile compute loop, 2 = skip the tile staging
+                     // copies, 4 = skip the tile stores (tile pipeline)
   TileArrays pt, ct; // gather tiles of the first / second operator (null when not tiled)
   int tile_slots;    // staging slots per CTA (dynamic shared memory holds tile_slots * 132 bytes)
   int tile_rows;     // tile pipeline: most rows of a tile, rounded up to 8
