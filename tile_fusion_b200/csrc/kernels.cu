@@ -220,6 +220,14 @@ __device__ __forceinline__ void sddmm_range_cta(const Params &P, int row, int p0
   }
 }
 
+// The next row of an item for this warp: rows go to whichever warp is free, so that a block with a few
+// long rows (power-law graphs) does not wait for the warp that drew them all.
+__device__ __forceinline__ int next_row(int *counter, int row_begin, int lane) {
+  int t = 0;
+  if (lane == 0) t = atomicAdd(counter, 1);
+  return row_begin + __shfl_sync(kFull, t, 0);
+}
+
 // ---------------------------------------------------------------------------
 // The persistent executor
 // ---------------------------------------------------------------------------
@@ -243,6 +251,7 @@ __global__ void __launch_bounds__(TILED ? tiled_threads(MODE) : kThreads, TILED 
   constexpr bool HAS_TC = MODE == 1 && TILED;  // the dense producer may run on the tensor cores
   __shared__ StreamSmem sm;
   __shared__ int s_next;
+  __shared__ int s_row;  // rows of the current item handed out so far (warps take the next row when they are free)
   __shared__ int s_ok;
   extern __shared__ float4 stage[];  // gather tiles: tile_slots * 8 float4, then tile_slots source row ids
   int *hrow = reinterpret_cast<int *>(stage + (size_t)P.tile_slots * 8);
@@ -255,7 +264,7 @@ __global__ void __launch_bounds__(TILED ? tiled_threads(MODE) : kThreads, TILED 
   const bool use_tc = HAS_TC && P.use_tc != 0;
   if (use_tc) tc_begin(tc);
 
-  if (threadIdx.x == 0) s_next = atomicAdd(&st->ticket, 1);
+  if (threadIdx.x == 0) { s_next = atomicAdd(&st->ticket, 1); s_row = 0; }
   __syncthreads();
   int cur = s_next;
   while (cur < n_items) {
@@ -306,8 +315,7 @@ __global__ void __launch_bounds__(TILED ? tiled_threads(MODE) : kThreads, TILED 
           spmm_row_cta<NT, VEC, CH, false, false>(P.f_ap, P.f_ai, P.f_ax, rb, P.in0, P.n_cols, dst_row(rb), false,
                                               0, 0, 0, sm.red);
         else {
-          const int q = (re - rb + NW - 1) / NW;  // consecutive rows per warp
-          for (int r = rb + warp * q; r < min(re, rb + (warp + 1) * q); ++r)
+          for (int r = next_row(&s_row, rb, lane); r < re; r = next_row(&s_row, rb, lane))
             spmm_row_warp<VEC, CH, false, false>(P.f_ap, P.f_ai, P.f_ax, r, P.in0, P.n_cols, dst_row(r),
                                                  false, 0, 0, 0, lane);
         }
@@ -323,8 +331,7 @@ __global__ void __launch_bounds__(TILED ? tiled_threads(MODE) : kThreads, TILED 
                                           P.out + (size_t)rb * P.n_cols, P.relu != 0, base, P.ring_rows,
                                           P.m_local, sm.red);
       else {
-        const int q = (re - rb + NW - 1) / NW;
-        for (int r = rb + warp * q; r < min(re, rb + (warp + 1) * q); ++r)
+        for (int r = next_row(&s_row, rb, lane); r < re; r = next_row(&s_row, rb, lane))
           spmm_row_warp<VEC, CH, true, RING>(P.s_ap, P.s_ai, P.s_ax, r, P.inter, P.n_cols,
                                              P.out + (size_t)r * P.n_cols, P.relu != 0, base, P.ring_rows,
                                              P.m_local, lane);
@@ -372,10 +379,10 @@ __global__ void __launch_bounds__(TILED ? tiled_threads(MODE) : kThreads, TILED 
       if (re - rb == 1 && __ldg(P.s_ap + re) - __ldg(P.s_ap + rb) >= kHeavyNnz) {
         sddmm_range_cta<NT, VEC, CH, false>(P, rb, __ldg(P.s_ap + rb), __ldg(P.s_ap + re), sm.red);
       } else
-      for (int r = rb + warp; r < re; r += NW) sddmm_row_warp<VEC, CH>(P, r, lane);
+      for (int r = next_row(&s_row, rb, lane); r < re; r = next_row(&s_row, rb, lane)) sddmm_row_warp<VEC, CH>(P, r, lane);
     }
     __syncthreads();
-    if (threadIdx.x == 0) s_next = nxt;
+    if (threadIdx.x == 0) { s_next = nxt; s_row = 0; }
     __syncthreads();
     cur = s_next;
   }
