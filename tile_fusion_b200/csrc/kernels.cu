@@ -234,7 +234,7 @@ __device__ __forceinline__ int next_row(int *counter, int row_begin, int lane) {
 #ifndef TF_MIN_CTAS
 #define TF_MIN_CTAS 4
 #endif
-constexpr int kHeavyNnz = 64 * kWarps;  // a single-row block at least this heavy is split over the CTA
+constexpr int kHeavyNnz = 32 * kWarps;  // a single-row block at least this heavy is split over the CTA
 
 union StreamSmem {
   GemmSmem g;

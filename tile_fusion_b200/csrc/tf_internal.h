@@ -21,7 +21,7 @@ constexpr int kDefaultTileSlotsSmall = kDefaultTileSlots;
 constexpr int kPipeTileSlots = 512;
 constexpr int kPipeTileRows = 256;
 constexpr int kDefaultTileMaxBz = 8;
-constexpr int kHeavyRowNnz = 512;    // a row at least this long is a block of its own (the CTA's warps share it)
+constexpr int kHeavyRowNnz = 256;    // a row at least this long is a block of its own (the CTA's warps share it)
 constexpr int kSegmentNnz = 4096;    // a row longer than this is cut into segments run by different CTAs
 constexpr bool kDefaultTileDoubleBuffer = false;
 constexpr int kTileMaxRows = 512;        // rows of a gather tile (16 per 8-lane group of a 256-thread CTA)
