@@ -29,6 +29,7 @@ constexpr int kPipeStagers = 128;  // 4 staging warps: 8 lanes per 128-byte slot
 constexpr int kPipeThreads = kPipeCompute + kPipeStagers + 32;  // + the control warp
 constexpr int kPipeStages = 3;     // chunk buffers: two fills are in flight while one chunk is computed
 constexpr int kPipeDepth = 4;      // tile descriptors in flight
+constexpr int kPipeDoneDepth = 4;  // compute warps are at most kPipeStages chunks, hence tiles, apart
 constexpr int kPipeReaders = (kPipeCompute + kPipeStagers) / 32;  // warps that read every descriptor
 constexpr int kPipeGroups = kPipeCompute / 4;
 constexpr int kPipeRounds = 3;     // rows per lane group: a tile holds at most 3 * 128 rows
@@ -42,7 +43,7 @@ struct PipeShared {
   unsigned long long desc_free[kPipeDepth];  // every reader warp has copied it
   int desc[kPipeDepth][8];               // kind (-1: no more work), flag index, tile, rows (rounded up to 8),
                                          // staged rows, their offset in the halo list, offset of the row table
-  int done_cnt[kPipeDepth];              // compute warps that finished the tile
+  int done_cnt[kPipeDoneDepth];          // compute warps that finished the tile
 };
 
 __device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
@@ -73,8 +74,8 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
     for (int i = 0; i < kPipeDepth; ++i) {
       mbar_init(&sh.desc_bar[i], 1);
       mbar_init(&sh.desc_free[i], kPipeReaders);
-      sh.done_cnt[i] = 0;
     }
+    for (int i = 0; i < kPipeDoneDepth; ++i) sh.done_cnt[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -256,7 +257,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
           // orders this warp's stores before the count within the CTA; the warp that publishes fences at
           // gpu scope, which covers everything that happened before its own increment
           __threadfence_block();
-          int *cntp = &sh.done_cnt[slot];
+          int *cntp = &sh.done_cnt[t & (kPipeDoneDepth - 1)];
           if (atomicAdd(cntp, 1) == kPipeCompute / 32 - 1) {
             *cntp = 0;
             publish(P.prod_done, block, P.epoch);
