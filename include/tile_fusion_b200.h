@@ -129,6 +129,10 @@ typedef struct {
   int tile_pipeline;      /* SpMM-SpMM with both operators tiled and no ring requested: 0 = run the tiles on
                              the role-split pipeline (one CTA per SM: staging warps copy the next column
                              chunk while compute warps work on the current one), <0 = never              */
+  int lattice_march;      /* SpMM-SpMM whose two operators are star stencils on one 3-D grid in natural order
+                             (every nonzero names the row's own grid point or one of its six neighbours):
+                             0 = run the plane-marching kernel, which keeps the intermediate in shared memory,
+                             <0 = never (general CSR path)                                               */
 } tf_plan_opts;
 
 typedef struct tf_plan tf_plan;
@@ -161,6 +165,16 @@ void tf_free(void *p);
  * row}.  No counterpart in the reference. */
 int tf_tiling_preview(const tf_csr *A, int tile_slots, int tile_max_bz, int **row_ptr, int **rows,
                       int **halo_ptr, int **halo, int *n_tiles, int info[4]);
+/* Host-only: how the library sees operator A (m x n CSR, of which the last `halo_rows` columns are halo rows
+ * appended after the local ones) as a star stencil on a 3-D grid in natural order -- the form the
+ * plane-marching executor runs from.  info = {recognised, nx, ny, nz, source planes below, source planes above,
+ * classes, 0}.  When recognised: dict = (classes + 1) x 8 floats, one coefficient vector per class in
+ * sorted-column order {z-, y-, x-, centre, x+, y+, z+, 0} (the last class is all zero); patch_cls =
+ * nz x ceil(ny/2) x ceil(nx/2) words holding the classes of the rows (2px+dx, 2py+dy, z) in byte 2*dy+dx;
+ * items = n_items x {x0, y0, z begin, z end, first column, flags}, the executor's work list for `n_cols`
+ * dense columns on `ctas` resident CTAs.  Arrays are malloc'd (tf_free).  No counterpart in the reference. */
+int tf_lattice_preview(const tf_csr *A, int halo_rows, int n_cols, int ctas, int info[8], float **dict,
+                       unsigned **patch_cls, int **items, int *n_items);
 /* info = {bx, by, bz, tiles} of the first operator's gather tiles, then the same for the second
  * operator's (zeros where an operator is not tiled). */
 int tf_plan_tile_info(const tf_plan *p, int info[8]);

@@ -34,7 +34,7 @@ class PlanOpts(C.Structure):
                 ("slack_blocks", C.c_int), ("ctas_per_sm", C.c_int), ("halo_rows", C.c_int),
                 ("n_boundary", C.c_int), ("boundary_rows", C.c_void_p), ("tile_slots", C.c_int),
                 ("tile_max_bz", C.c_int), ("tile_double_buffer", C.c_int), ("tensor_cores", C.c_int),
-                ("tile_pipeline", C.c_int)]
+                ("tile_pipeline", C.c_int), ("lattice_march", C.c_int)]
 
 
 EXPORTS = [
@@ -44,7 +44,7 @@ EXPORTS = [
     "tf_plan_info", "tf_plan_status", "tf_exec_spmm_spmm", "tf_exec_gemm_spmm", "tf_exec_sddmm_spmm",
     "tf_exec_phase", "tf_plan_intermediate", "tf_plan_exchange_buffers", "tf_spmm_spmm_host", "tf_gemm_spmm_host",
     "tf_sddmm_spmm_host", "tf_spmm_dev", "tf_fill_uniform", "tf_fill_normal", "tf_plan_preview", "tf_free", "tf_plan_set_wait_limit", "tf_tiling_preview", "tf_plan_tile_info", "tf_spmm_spmm_noalloc",
-    "tf_noalloc_max_floats", "tf_gemm_tc_dev",
+    "tf_noalloc_max_floats", "tf_gemm_tc_dev", "tf_lattice_preview",
 ]
 
 _lib = None
@@ -102,6 +102,7 @@ def lib() -> C.CDLL:
     L.tf_noalloc_max_floats.restype = C.c_longlong
     L.tf_gemm_tc_dev.argtypes = [vp, vp, i, i, i, i, vp, vp]
     L.tf_free.restype = None
+    L.tf_lattice_preview.argtypes = [C.POINTER(Csr), i, i, i, ip, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), ip]
     _lib = L
     return L
 

@@ -187,14 +187,14 @@ class Plan:
                  mode: int = MODE_STREAM, schedule: FusedSchedule | None = None, rows_per_block: int = 0,
                  ring_bytes: int = 0, slack_blocks: int = -1, ctas_per_sm: int = 0, halo_rows: int = 0,
                  boundary_rows=None, tile_slots: int = 0, tile_max_bz: int = 0, tensor_cores: int = 0,
-                 tile_double_buffer: int = 0, tile_pipeline: int = 0):
+                 tile_double_buffer: int = 0, tile_pipeline: int = 0, lattice_march: int = 0):
         L = _lib.lib()
         self.chain, self.A, self.B = chain, A, B
         self.n_cols, self.k = int(n_cols), int(k)
         br = _i32(boundary_rows) if boundary_rows is not None and len(boundary_rows) else None
         o = _lib.PlanOpts(mode, rows_per_block, ring_bytes, slack_blocks, ctas_per_sm, halo_rows,
                           0 if br is None else br.shape[0], None if br is None else br.ctypes.data,
-                          tile_slots, tile_max_bz, tile_double_buffer, tensor_cores, tile_pipeline)
+                          tile_slots, tile_max_bz, tile_double_buffer, tensor_cores, tile_pipeline, lattice_march)
         h = C.c_void_p()
         ca = A._c()
         sh = schedule._h if schedule is not None else None
@@ -375,7 +375,7 @@ def plan_preview(A: CSRMatrix, B: CSRMatrix | None = None, *, producer_is_gemm=F
     {kind, block, row_begin, row_end, need, base, aux0, aux1}, plus an info dict."""
     br = _i32(boundary_rows) if boundary_rows is not None and len(boundary_rows) else None
     o = _lib.PlanOpts(mode, rows_per_block, ring_bytes, slack_blocks, 0, halo_rows,
-                      0 if br is None else br.shape[0], None if br is None else br.ctypes.data, tile_slots, tile_max_bz, 0, 0, 0)
+                      0 if br is None else br.shape[0], None if br is None else br.ctypes.data, tile_slots, tile_max_bz, 0, 0, 0, 0)
     ca = A._c()
     cb = B._c() if B is not None else None
     items, n = C.c_void_p(), C.c_longlong()
@@ -410,3 +410,27 @@ def tiling_preview(A: CSRMatrix, tile_slots=0, tile_max_bz=0):
     halo_ptr = take(halo_ptr_raw, n.value + 1)
     halo = take(ptrs[3], int(halo_ptr[-1]))
     return row_ptr, rows, halo_ptr, halo, dict(bx=info[0], by=info[1], bz=info[2], reuse=info[3] / 1000.0)
+
+
+def lattice_preview(A: CSRMatrix, halo_rows=0, n_cols=128, ctas=148):
+    """Host-only: operator A as a star stencil on a 3-D grid (what the plane-marching executor runs from), or None
+    when the pattern is not one.  Returns dict(nx, ny, nz, ghost_lo, ghost_hi, classes, dict, patch_cls, items)."""
+    ca = A._c()
+    info = (C.c_int * 8)()
+    d, pc, it = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    n = C.c_int()
+    check(_lib.lib().tf_lattice_preview(C.byref(ca), int(halo_rows), int(n_cols), int(ctas), info, C.byref(d),
+                                        C.byref(pc), C.byref(it), C.byref(n)))
+    if not info[0]:
+        return None
+    nx, ny, nz, ncls = info[1], info[2], info[3], info[6]
+
+    def take(p, ctype, count, dtype):
+        arr = np.ctypeslib.as_array(C.cast(p, C.POINTER(ctype)), shape=(max(count, 1),)).copy()[:count].astype(dtype)
+        _lib.lib().tf_free(p)
+        return arr
+    dic = take(d, C.c_float, (ncls + 1) * 8, np.float32).reshape(ncls + 1, 8)
+    pcl = take(pc, C.c_uint, nz * ((ny + 1) // 2) * ((nx + 1) // 2), np.uint32).reshape(nz, (ny + 1) // 2, (nx + 1) // 2)
+    items = take(it, C.c_int, 6 * n.value, np.int32).reshape(-1, 6)
+    return dict(nx=nx, ny=ny, nz=nz, ghost_lo=info[4], ghost_hi=info[5], classes=ncls, dict=dic, patch_cls=pcl,
+                items=items)

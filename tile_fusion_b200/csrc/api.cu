@@ -10,6 +10,7 @@
 
 #include "gemm_tc_host.h"
 #include "kernels.cuh"
+#include "lattice_march.h"
 #include "launch.h"
 #include "tf_internal.h"
 
@@ -134,6 +135,17 @@ struct tf_plan {
   DevBuf<float> w_hi, w_lo;  // split, transposed weight [n_cols][k]
   CUtensorMap tm_whi, tm_wlo;
   int tile_info[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // producer bx,by,bz,tiles ; consumer bx,by,bz,tiles
+  // plane-marching executor (both operators are star stencils on one grid)
+  struct March {
+    bool on = false;
+    int nx = 0, ny = 0, nz = 0, ncls_f = 0, ncls_a = 0, z_shift = 0, grid = 0, n_items = 0;
+    long long planes_c = 0;
+    DevBuf<unsigned> pcls_f, pcls_a;
+    DevBuf<float> dict_f, dict_a;
+    DevBuf<int4> items;
+    DevBuf<tfk::MarchState> st;
+    std::vector<tf::MarchItem> host_items;
+  } march;
   // schedule mode
   DevBuf<int> s_ptr2, s_id, s_type, s_ker;
   int s_n1 = 0;
@@ -281,6 +293,76 @@ int load_schedule(tf_plan &p, const tf_schedule *s, bool need_ker) {
 }
 
 void build_segments(tf_plan &p, int n_seg);
+
+static_assert(tf::kMarchMaxClasses == tfk::kMarchMaxClassesDev, "host and device class limits differ");
+
+// Plane-marching executor: taken when both operators of an SpMM-SpMM chain are star stencils on the same
+// grid (lattice.cpp).  The general plan is built as well and serves calls whose operands are not 16-byte
+// aligned.
+int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int sm_count) {
+  tf::LatticeOp lf, la;
+  int rc = tf::analyse_lattice_operator(F.m, F.n, F.ap, F.ai, F.ax, 0, lf);
+  if (rc != TF_OK || !lf.ok) return rc;
+  if (&F == &A) la = lf;
+  else {
+    rc = tf::analyse_lattice_operator(A.m, A.n, A.ap, A.ai, A.ax, 0, la);
+    if (rc != TF_OK || !la.ok) return rc;
+  }
+  if (la.nx != lf.nx || la.ny != lf.ny || la.nz != lf.nz || la.ghost_lo || la.ghost_hi) return TF_OK;
+  tf_plan::March &M = p.march;
+  M.nx = lf.nx; M.ny = lf.ny; M.nz = lf.nz;
+  M.ncls_f = lf.n_classes; M.ncls_a = la.n_classes;
+  M.z_shift = lf.ghost_lo;
+  M.planes_c = (long long)lf.nz + lf.ghost_lo + lf.ghost_hi;
+  M.grid = sm_count;
+  tf::build_march_items(M.nx, M.ny, 0, M.nz, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, M.grid, 1,
+                        M.host_items);
+  std::vector<int4> raw(2 * M.host_items.size());
+  for (size_t i = 0; i < M.host_items.size(); ++i) {
+    const tf::MarchItem &it = M.host_items[i];
+    raw[2 * i] = make_int4(it.x0, it.y0, it.zs, it.ze);
+    raw[2 * i + 1] = make_int4(it.c0, it.flags, 0, 0);
+  }
+  M.n_items = (int)M.host_items.size();
+  rc = M.items.upload(raw);
+  if (rc == TF_OK) rc = M.pcls_f.upload(lf.patch_cls);
+  if (rc == TF_OK) rc = M.dict_f.upload(lf.dict);
+  if (rc == TF_OK) rc = M.pcls_a.upload(la.patch_cls);
+  if (rc == TF_OK) rc = M.dict_a.upload(la.dict);
+  if (rc == TF_OK) rc = M.st.alloc(1);
+  if (rc != TF_OK) return rc;
+  TF_CUDA(cudaMemset(M.st.p, 0, sizeof(tfk::MarchState)));
+  M.on = true;
+  return TF_OK;
+}
+
+bool aligned(const void *q, size_t a);
+
+// One launch over the march items [item_begin, item_end).
+int run_march(tf_plan &p, const float *C, float *D, int item_begin, int item_end, cudaStream_t s) {
+  tf_plan::March &M = p.march;
+  CUtensorMap tm;
+  const int mr = tfk::march_make_map(&tm, C, p.n_cols, M.nx, M.ny, M.planes_c);
+  if (mr != 0) return fail(TF_ERR_CUDA, "cuTensorMapEncodeTiled failed for the dense operand (code " + std::to_string(mr) + ")");
+  tfk::MarchParams Q;
+  std::memset(&Q, 0, sizeof(Q));
+  Q.pcls_f = M.pcls_f.p; Q.pcls_a = M.pcls_a.p;
+  Q.dict_f = reinterpret_cast<const float4 *>(M.dict_f.p);
+  Q.dict_a = reinterpret_cast<const float4 *>(M.dict_a.p);
+  Q.ncls_f = M.ncls_f; Q.ncls_a = M.ncls_a;
+  Q.out = D;
+  Q.items = M.items.p;
+  Q.item_begin = item_begin; Q.item_end = item_end;
+  Q.st = M.st.p;
+  Q.nx = M.nx; Q.ny = M.ny; Q.nz = M.nz;
+  Q.pnx = (M.nx + 1) / 2; Q.pny = (M.ny + 1) / 2;
+  Q.n_cols = p.n_cols;
+  Q.z_shift = M.z_shift;
+  Q.wait_limit = p.spin_limit;
+  TF_CUDA(tfk::launch_lattice_march(std::min(M.grid, std::max(1, item_end - item_begin)), tm, Q, s));
+  p.launches = 1;
+  return TF_OK;
+}
 
 // Common plan construction for the two-operator chains.
 int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int n_cols, const tf_plan_opts *opts,
@@ -451,6 +533,11 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
     rc = load_schedule(*p, sched, chain == 1);
     if (rc != TF_OK) return rc;
   }
+  if (chain == 0 && F && o.mode == TF_MODE_STREAM && o.lattice_march >= 0 && o.ring_bytes <= 0 && !o.halo_rows &&
+      !o.n_boundary && n_cols % 4 == 0) {
+    rc = build_march(*p, *F, *A, sm_count);
+    if (rc != TF_OK) return rc;
+  }
   *out = p.release();
   return TF_OK;
 }
@@ -479,6 +566,7 @@ tfk::Params base_params(tf_plan &p) {
 }
 
 bool aligned(const void *q, size_t a) { return (reinterpret_cast<uintptr_t>(q) % a) == 0; }
+bool march_usable(const tf_plan &p, const float *C, const float *D) { return p.march.on && aligned(C, 16) && aligned(D, 16); }
 
 // vector width usable with the caller's pointers (plan-owned buffers are always aligned)
 void call_shape(const tf_plan &p, std::initializer_list<const void *> ptrs, int *vec, int *ch) {
@@ -736,8 +824,8 @@ int tf_plan_info(const tf_plan *p, long long info[8]) {
   info[1] = p->hp.n_prod;
   info[2] = p->hp.n_cons;
   info[3] = p->hp.ring_rows;
-  info[4] = p->pipe ? p->pipe_grid : p->grid;
-  info[5] = p->pipe ? 672 : (p->dyn_smem > 0 ? tfk::tiled_threads(p->chain) : tfk::kThreads);
+  info[4] = p->march.on ? p->march.grid : (p->pipe ? p->pipe_grid : p->grid);
+  info[5] = p->march.on ? tfk::kMarchThreads : (p->pipe ? 672 : (p->dyn_smem > 0 ? tfk::tiled_threads(p->chain) : tfk::kThreads));
   info[6] = p->launches;
   info[7] = p->hp.inter_rows;
   return TF_OK;
@@ -760,6 +848,14 @@ int tf_plan_status(tf_plan *p, void *stream) {
   int rc = set_device(*p);
   if (rc != TF_OK) return rc;
   TF_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  if (p->march.on) {
+    tfk::MarchState ms;
+    TF_CUDA(cudaMemcpy(&ms, p->march.st.p, sizeof(ms), cudaMemcpyDeviceToHost));
+    if (ms.error) {
+      cudaMemset(p->march.st.p, 0, sizeof(ms));
+      return fail(TF_ERR_TIMEOUT, "a bounded in-kernel wait ran out; the output of the last call is not valid");
+    }
+  }
   tfk::ExecState st;
   TF_CUDA(cudaMemcpy(&st, p->state.p, sizeof(st), cudaMemcpyDeviceToHost));
   if (st.error) {
@@ -776,6 +872,7 @@ int tf_exec_spmm_spmm(tf_plan *p, const float *C, float *D, void *stream) {
   if (p->halo_rows || p->sendbuf.n) return fail(TF_ERR_ARG, "tf_exec_spmm_spmm: plan has halo rows, drive it with tf_exec_phase");
   int rc = set_device(*p);
   if (rc != TF_OK) return rc;
+  if (march_usable(*p, C, D)) return run_march(*p, C, D, 0, p->march.n_items, (cudaStream_t)stream);
   tfk::Params P = base_params(*p);
   P.in0 = C; P.out = D;
   return run_chain(*p, P, (cudaStream_t)stream);

@@ -47,6 +47,43 @@ struct Item {
   int aux0, aux1;
 };
 
+// Lattice structure of a pattern: the dominant column offsets are 1, nx and nx*ny around the operator's
+// own diagonal, which sits `shift` columns right of the row index (0 for a square operator; a constant
+// when the columns were renumbered, as for one rank's rows of a partitioned chain).
+struct Lattice {
+  int dims = 0;  // 0 = none
+  int nx = 0, ny = 0;
+  int shift = 0;
+};
+Lattice detect_lattice(int m, const int *ap, const int *ai);
+
+// An operator verified to be a star stencil (at most the 7 points 0, +-1, +-nx, +-nx*ny, never across a
+// grid edge) on an nx x ny x nz lattice in natural order, with its rows classified by coefficient vector
+// (see lattice.cpp).  This is what the plane-marching executor runs from instead of the CSR arrays.
+constexpr int kMarchMaxClasses = 63;
+struct LatticeOp {
+  bool ok = false;
+  int nx = 0, ny = 0, nz = 0;
+  int ghost_lo = 0, ghost_hi = 0;  // planes of the source operand below / above the operator's own rows
+  int n_classes = 0;               // distinct coefficient vectors; class n_classes is the all-zero vector
+  std::vector<float> dict;         // (n_classes + 1) x 8: {z-, y-, x-, centre, x+, y+, z+, 0} -- CSR order
+  std::vector<uint32_t> patch_cls; // [nz][ceil(ny/2)][ceil(nx/2)]: classes of the rows (2px+dx, 2py+dy, z), byte 2*dy+dx
+};
+// halo_lo / halo_hi: rows of source planes that are not addressed as shifted lattice neighbours but are
+// appended after the m local rows (the second operator of a partitioned chain): lower plane first.
+int analyse_lattice_operator(int m, int ncols, const int *ap, const int *ai, const float *ax, int halo_rows,
+                             LatticeOp &out);
+
+// Work items of the plane-marching executor: an x-y tile, a range of planes and a column chunk each.
+struct MarchItem {
+  int x0, y0, zs, ze, c0, flags;
+};
+// tile_w x tile_h tiles, chunks of `chunk` columns; planes [z_begin, z_end) cut into the number of segments
+// that finishes soonest on `ctas` resident CTAs.  Order: segment, tile, chunk (chunks of a tile adjacent, so
+// that concurrently running CTAs read whole dense rows and neighbouring tiles together).
+void build_march_items(int nx, int ny, int z_begin, int z_end, int n_cols, int tile_w, int tile_h, int chunk,
+                       int ctas, int min_segments, std::vector<MarchItem> &out);
+
 // Partition of an operator's rows into gather tiles (see tiling.cpp).
 struct Tiling {
   bool tiled = false, failed = false;

@@ -15,13 +15,6 @@
 
 namespace tf {
 
-namespace {
-
-struct Lattice {
-  int dims = 0;  // 0 = none
-  int nx = 0, ny = 0;
-};
-
 Lattice detect_lattice(int m, const int *ap, const int *ai) {
   Lattice L;
   std::unordered_map<int, int> hist;
@@ -40,6 +33,7 @@ Lattice detect_lattice(int m, const int *ap, const int *ai) {
   std::sort(freq.begin(), freq.end());
   if (freq.empty() || freq.size() % 2 == 0) return L;
   const int d0 = freq[freq.size() / 2];
+  L.shift = d0;
   std::vector<int> pos;
   for (int f : freq)
     if (f > d0) pos.push_back(f - d0);
@@ -53,8 +47,6 @@ Lattice detect_lattice(int m, const int *ap, const int *ai) {
   if (L.dims == 1) L.nx = m;
   return L;
 }
-
-}  // namespace
 
 int build_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_bz, int max_rows, Tiling &out) {
   out = Tiling();
