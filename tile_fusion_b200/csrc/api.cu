@@ -314,7 +314,9 @@ int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int sm_count) {
   M.ncls_f = lf.n_classes; M.ncls_a = la.n_classes;
   M.z_shift = lf.ghost_lo;
   M.planes_c = (long long)lf.nz + lf.ghost_lo + lf.ghost_hi;
-  M.grid = sm_count;
+  const int occ = tfk::march_ctas_per_sm();
+  if (occ <= 0) return TF_OK;  // the kernel does not fit this device: general path
+  M.grid = sm_count * occ;
   tf::build_march_items(M.nx, M.ny, 0, M.nz, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, M.grid, 1,
                         M.host_items);
   std::vector<int4> raw(2 * M.host_items.size());

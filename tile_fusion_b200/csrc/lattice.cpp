@@ -181,7 +181,7 @@ extern "C" int tf_lattice_preview(const tf_csr *A, int halo_rows, int n_cols, in
   std::copy(op.dict.begin(), op.dict.end(), *dict);
   std::copy(op.patch_cls.begin(), op.patch_cls.end(), *patch_cls);
   std::vector<tf::MarchItem> it;
-  tf::build_march_items(op.nx, op.ny, 0, op.nz, n_cols, 16, 16, 16, ctas > 0 ? ctas : 148, 1, it);
+  tf::build_march_items(op.nx, op.ny, 0, op.nz, n_cols, 16, 8, 16, ctas > 0 ? ctas : 296, 1, it);
   *n_items = (int)it.size();
   *items = (int *)malloc(sizeof(int) * 6 * std::max<size_t>(it.size(), 1));
   if (!*items) return tf::fail(TF_ERR_NOMEM, "tf_lattice_preview: out of memory");

@@ -28,6 +28,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "lattice_march.h"
 
 namespace tfk {
@@ -37,17 +39,15 @@ namespace {
 constexpr int W = kMarchW, H = kMarchH;
 constexpr int PC = W + 4;  // pitch (rows) of the staged C rectangle
 constexpr int PT = W + 2;  // pitch of the T rectangle
-constexpr unsigned kFullMask = 0xffffffffu;
 
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned long long *bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+__device__ __forceinline__ void mbar_init(unsigned bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity, int limit) {
-  const unsigned a = smem_u32(bar);
+__device__ __forceinline__ bool mbar_wait(unsigned a, unsigned parity, int limit) {
   for (int i = 0; i < limit; ++i) {
     unsigned done;
     asm volatile(
@@ -60,11 +60,11 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned pari
   return false;
 }
 // One plane of C for a tile: coordinates (column, x / 2, x % 2, y, plane).
-__device__ __forceinline__ void tma_load_plane(void *smem, const CUtensorMap *tm, int col, int xh, int y, int z,
-                                               unsigned long long *bar) {
+__device__ __forceinline__ void tma_load_plane(unsigned smem, const CUtensorMap *tm, int col, int xh, int y, int z,
+                                               unsigned bar) {
   asm volatile(
       "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-      ::"r"(smem_u32(smem)), "l"((unsigned long long)tm), "r"(smem_u32(bar)), "r"(col), "r"(xh), "r"(0), "r"(y), "r"(z)
+      ::"r"(smem), "l"((unsigned long long)tm), "r"(bar), "r"(col), "r"(xh), "r"(0), "r"(y), "r"(z)
       : "memory");
 }
 
@@ -73,323 +73,355 @@ __device__ __forceinline__ void tma_load_plane(void *smem, const CUtensorMap *tm
 template <int P>
 __device__ __forceinline__ int xoff(int rx) { return (rx & 1) * (P / 2 * 64) + (rx >> 1) * 64; }
 
-__device__ __forceinline__ float4 lds4(const char *buf, int off) { return *reinterpret_cast<const float4 *>(buf + off); }
-__device__ __forceinline__ void sts4(char *buf, int off, const float4 &v) { *reinterpret_cast<float4 *>(buf + off) = v; }
+// Shared memory is addressed by 32-bit shared-window addresses throughout (ld.shared / st.shared).
+__device__ __forceinline__ float4 lds4(unsigned buf, int off) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(buf + off) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts4(unsigned buf, int off, const float4 &v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(buf + off), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
 __device__ __forceinline__ float4 fma4(float a, const float4 &x, const float4 &c) {
   return make_float4(fmaf(a, x.x, c.x), fmaf(a, x.y, c.y), fmaf(a, x.z, c.z), fmaf(a, x.w, c.w));
 }
 __device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.f); }
 
-struct Coef {
-  float zm, ym, xm, c0, xp, yp, zp;
-};
-__device__ __forceinline__ Coef coef_from(const float4 &a, const float4 &b) {
-  return Coef{a.x, a.y, a.z, a.w, b.x, b.y, b.z};
-}
-
-// Own rows and in-plane neighbours of a PX x PY patch in a rectangle of pitch P.  xo[a + 1] = byte offset of
-// the patch's column a (-1 .. PX) inside a y-row, lane's 16 bytes included; yo = byte offset of the patch's
-// first y-row.  nb: [0, PY) left column, [PY, 2PY) right column, [2PY, 2PY+PX) row below, then the row above.
-template <int PX, int PY, int P>
-__device__ __forceinline__ void load_nb(const char *buf, const int (&xo)[PX + 2], int yo, float4 (&nb)[2 * PX + 2 * PY]) {
+// In-plane neighbours of a 2 x 2 patch in a rectangle of pitch P.  xo[a + 1] = byte offset of the patch's
+// column a (-1 .. 2) inside a y-row, lane's 16 bytes included; yo = byte offset of the patch's first y-row.
+// nb: [0, 2) left column, [2, 4) right column, [4, 6) row below, [6, 8) row above.
+template <int P>
+__device__ __forceinline__ void load_nb(unsigned buf, const int (&xo)[4], int yo, float4 (&nb)[8]) {
 #pragma unroll
-  for (int b = 0; b < PY; ++b) {
+  for (int b = 0; b < 2; ++b) {
     nb[b] = lds4(buf, yo + b * (P * 64) + xo[0]);
-    nb[PY + b] = lds4(buf, yo + b * (P * 64) + xo[PX + 1]);
+    nb[2 + b] = lds4(buf, yo + b * (P * 64) + xo[3]);
   }
 #pragma unroll
-  for (int a = 0; a < PX; ++a) {
-    nb[2 * PY + a] = lds4(buf, yo - P * 64 + xo[a + 1]);
-    nb[2 * PY + PX + a] = lds4(buf, yo + PY * (P * 64) + xo[a + 1]);
+  for (int a = 0; a < 2; ++a) {
+    nb[4 + a] = lds4(buf, yo - P * 64 + xo[a + 1]);
+    nb[6 + a] = lds4(buf, yo + 2 * (P * 64) + xo[a + 1]);
   }
 }
-template <int PX, int PY, int P>
-__device__ __forceinline__ void load_own(const char *buf, const int (&xo)[PX + 2], int yo, float4 (&own)[PX * PY]) {
+template <int P>
+__device__ __forceinline__ void load_own(unsigned buf, const int (&xo)[4], int yo, float4 (&own)[4]) {
 #pragma unroll
-  for (int b = 0; b < PY; ++b)
-#pragma unroll
-    for (int a = 0; a < PX; ++a) own[b * PX + a] = lds4(buf, yo + b * (P * 64) + xo[a + 1]);
+  for (int j = 0; j < 4; ++j) own[j] = lds4(buf, yo + (j >> 1) * (P * 64) + xo[(j & 1) + 1]);
 }
 
-// acc[j] = the first six products of row j in sorted-column order: z- (from `prev`, the same grid point
-// one plane down), y-, x-, centre, x+, y+ (this plane).  The z+ product is added one step later.
-template <int PX, int PY>
-__device__ __forceinline__ void stencil_partial(float4 (&acc)[PX * PY], const float4 (&prev)[PX * PY],
-                                                const float4 (&own)[PX * PY], const float4 (&nb)[2 * PX + 2 * PY],
-                                                const Coef (&cf)[PX * PY]) {
-#pragma unroll
-  for (int b = 0; b < PY; ++b)
-#pragma unroll
-    for (int a = 0; a < PX; ++a) {
-      const int j = b * PX + a;
-      float4 s = fma4(cf[j].zm, prev[j], zero4());
-      s = fma4(cf[j].ym, b > 0 ? own[j - PX] : nb[2 * PY + a], s);
-      s = fma4(cf[j].xm, a > 0 ? own[j - 1] : nb[b], s);
-      s = fma4(cf[j].c0, own[j], s);
-      s = fma4(cf[j].xp, a < PX - 1 ? own[j + 1] : nb[PY + b], s);
-      s = fma4(cf[j].yp, b < PY - 1 ? own[j + PX] : nb[2 * PY + PX + a], s);
-      acc[j] = s;
-    }
+// Starts one row: acc = its first six products in sorted-column order -- z- (from `zm`, the same grid point one
+// plane down), y-, x-, centre, x+, y+ (this plane); the z+ product is added one step later with the returned
+// coefficient.  The coefficients are entry `cls` of a dictionary in shared memory (two 16-byte loads that
+// the lanes of a warp mostly share).
+__device__ __forceinline__ float row_start(float4 &acc, unsigned dict, unsigned cls, const float4 &zm, const float4 &ym,
+                                           const float4 &xm, const float4 &c, const float4 &xp, const float4 &yp) {
+  const float4 lo = lds4(dict, 32 * cls), hi = lds4(dict, 32 * cls + 16);
+  float4 s = fma4(lo.x, zm, zero4());
+  s = fma4(lo.y, ym, s);
+  s = fma4(lo.z, xm, s);
+  s = fma4(lo.w, c, s);
+  s = fma4(hi.x, xp, s);
+  acc = fma4(hi.y, yp, s);
+  return hi.z;
+}
+// The four rows of a 2 x 2 patch; class of row j = byte j of `word`.
+__device__ __forceinline__ void patch_start(float4 (&acc)[4], float (&czp)[4], unsigned dict, unsigned word,
+                                            const float4 (&prev)[4], const float4 (&own)[4], const float4 (&nb)[8]) {
+  czp[0] = row_start(acc[0], dict, word & 255u, prev[0], nb[4], nb[0], own[0], own[1], own[2]);
+  czp[1] = row_start(acc[1], dict, (word >> 8) & 255u, prev[1], nb[5], own[0], own[1], nb[2], own[3]);
+  czp[2] = row_start(acc[2], dict, (word >> 16) & 255u, prev[2], own[0], nb[1], own[2], own[3], nb[6]);
+  czp[3] = row_start(acc[3], dict, word >> 24, prev[3], own[1], own[2], own[3], nb[3], nb[7]);
 }
 
-// Class word of the patch that holds grid point (x, y) of plane z: classes of (2px+dx, 2py+dy), byte
-// 2*dy+dx.  Outside the grid every row is of the zero class.
-__device__ __forceinline__ unsigned class_word(const unsigned *pcls, int x, int y, int z, int nx, int ny, int nz,
-                                               int pnx, int pny, unsigned zero_word) {
-  if (x < 0 || x >= nx || y < 0 || y >= ny || z < 0 || z >= nz) return zero_word;
-  return __ldg(pcls + ((size_t)z * pny + (y >> 1)) * pnx + (x >> 1));
-}
-
-// Coefficients of the PX x PY rows of a patch at (x, y) from its class word.
-template <int PX, int PY>
-__device__ __forceinline__ void patch_coefs(Coef (&cf)[PX * PY], unsigned word, int x, int y, const float4 *dict,
-                                            const Coef &c0) {
-  if (__all_sync(kFullMask, word == 0u)) {
-#pragma unroll
-    for (int j = 0; j < PX * PY; ++j) cf[j] = c0;
-    return;
+// Class words of one patch column: the word of plane z, or the all-zero class outside the grid.
+struct ClassColumn {
+  const unsigned *p;  // word of plane 0 (valid only when inside)
+  unsigned zero_word;
+  int plane_words, nz;
+  bool inside;
+  __device__ __forceinline__ void init(const unsigned *pcls, int x, int y, int nx, int ny, int nz_, int pnx, int pny,
+                                       unsigned zero) {
+    inside = x >= 0 && x < nx && y >= 0 && y < ny;
+    p = pcls + (inside ? (y >> 1) * pnx + (x >> 1) : 0);
+    plane_words = pnx * pny; nz = nz_; zero_word = zero;
   }
-#pragma unroll
-  for (int b = 0; b < PY; ++b)
-#pragma unroll
-    for (int a = 0; a < PX; ++a) {
-      const int byte = 2 * ((y + b) & 1) + ((x + a) & 1);
-      const unsigned c = (word >> (8 * byte)) & 255u;
-      cf[b * PX + a] = coef_from(dict[2 * c], dict[2 * c + 1]);
-    }
-}
-
-struct Shared {
-  char *cbuf, *tbuf;
-  float4 *dict_f, *dict_a;
-  unsigned long long *full;
+  __device__ __forceinline__ unsigned at(int z) const {
+    return (inside && (unsigned)z < (unsigned)nz) ? __ldg(p + (size_t)z * plane_words) : zero_word;
+  }
 };
 
-// The border ring of T: a PX x PY strip at (x, y), first-operator work only.
-template <int PX, int PY>
-__device__ __forceinline__ bool march_border(const MarchParams &P, const Shared &S, int x, int y, int x0, int y0,
-                                             int kfirst, int steps, int c0col, int c4, unsigned &n_use,
-                                             const Coef &cF0) {
-  int xoC[PX + 2], xoT[PX + 2];
+// 32-bit shared-window addresses of the CTA's buffers.
+struct Shared {
+  unsigned cbuf, tbuf;       // C stages, the two planes of T
+  unsigned dict_f, dict_a;   // (classes + 1) x 32 bytes each
+  unsigned full;             // mbarriers, 8 bytes each: one per C stage (the plane has landed)
+  unsigned tbar;             // one phase per step: every warp has stored its rows of T(k-1) (and read C(k))
+  volatile int *abort;
+};
+
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait that also gives up when another thread of the CTA already has.
+__device__ __forceinline__ bool wait_or_abort(unsigned a, unsigned parity, int limit, volatile int *abort) {
+  for (int i = 0; i < limit; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(a), "r"(parity) : "memory");
+    if (done) return true;
+    if ((i & 255) == 255 && *abort) break;
+  }
+  *abort = 1;
+  return false;
+}
+
+// One row of T(k-1) from the neighbour rank's plane (k-1 lies outside this rank's planes).
+__device__ __forceinline__ float4 halo_row(const float *halo, int gx, int gy, int col, const MarchParams &P) {
+  if (gx >= 0 && gx < P.nx && gy >= 0 && gy < P.ny && col < P.n_cols)
+    return __ldg(reinterpret_cast<const float4 *>(halo + ((size_t)gy * P.nx + gx) * P.n_cols + col));
+  return zero4();
+}
+
+// State a CTA carries from item to item.
+struct CtaState {
+  unsigned n_use;  // steps taken so far: step n uses C stage n % stages (parity of n / stages) and phase n of tbar
+  unsigned n_iss;  // plane loads issued so far (thread 0 issues them)
+};
+
+// Rows of the ring of T around the tile that one 4-lane group computes besides its patch.
+constexpr int kRing = (2 * W + 2 * H + (W / 2) * (H / 2) - 1) / ((W / 2) * (H / 2));
+
+// One work item, seen by one thread: its 2 x 2 patch of the tile at (x, y) (both products) and kRing single
+// rows of the ring of T around the tile at (rx[r], ry[r]) (first product only; `ring` = this warp has any).
+__device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchParams &P, const Shared &S, CtaState &cs,
+                                         int x0, int y0, int zs, int ze, int c0col, int x, int y, bool ring,
+                                         const int (&rx)[kRing], const int (&ry)[kRing]) {
+  const int tid = threadIdx.x, lane = tid & 31, c4 = lane & 3;
+  const int kfirst = zs - 2, steps = ze - zs + 4;
+  int xoC[4], xoT[4];
 #pragma unroll
-  for (int a = -1; a <= PX; ++a) {
+  for (int a = -1; a <= 2; ++a) {
     xoC[a + 1] = xoff<PC>(x - x0 + 2 + a) + c4 * 16;
     xoT[a + 1] = xoff<PT>(x - x0 + 1 + a) + c4 * 16;
   }
   const int yoC = (y - y0 + 2) * (PC * 64), yoT = (y - y0 + 1) * (PT * 64);
-  const unsigned zero_f = 0x01010101u * (unsigned)P.ncls_f;
-  float4 cprev[PX * PY], accT[PX * PY];
-  float czp[PX * PY];
+  // ring rows: offsets of the row and of its left / right neighbour in the C rectangle, of the row in the T one
+  int roC[kRing], roL[kRing], roR[kRing], roT[kRing];
+  unsigned rsh[kRing];  // bit position of the row's class in its patch's class word
+  ClassColumn cr_col[kRing];
 #pragma unroll
-  for (int j = 0; j < PX * PY; ++j) { cprev[j] = zero4(); accT[j] = zero4(); czp[j] = 0.f; }
-  unsigned wf = class_word(P.pcls_f, x, y, kfirst, P.nx, P.ny, P.nz, P.pnx, P.pny, zero_f);
-  const int zs = kfirst + 2, ze = kfirst + steps - 2;
-  for (int step = 0; step < steps; ++step, ++n_use) {
+  for (int r = 0; r < kRing; ++r) {
+    const int yb = (ry[r] - y0 + 2) * (PC * 64) + c4 * 16;
+    roC[r] = yb + xoff<PC>(rx[r] - x0 + 2);
+    roL[r] = yb + xoff<PC>(rx[r] - x0 + 1);
+    roR[r] = yb + xoff<PC>(rx[r] - x0 + 3);
+    roT[r] = (ry[r] - y0 + 1) * (PT * 64) + xoff<PT>(rx[r] - x0 + 1) + c4 * 16;
+    rsh[r] = 8u * (2u * (ry[r] & 1) + (rx[r] & 1));
+    cr_col[r].init(P.pcls_f, rx[r], ry[r], P.nx, P.ny, P.nz, P.pnx, P.pny, 0x01010101u * (unsigned)P.ncls_f);
+  }
+  const int col = c0col + 4 * c4;
+  // rows of the patch that exist and whose columns exist: bit j
+  unsigned live = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (x + (j & 1) < P.nx && y + (j >> 1) < P.ny && col < P.n_cols) live |= 1u << j;
+  // D row (x, y) of plane k - 2 at step k; rows of the patch are n_cols and nx * n_cols floats further
+  const size_t plane_floats = (size_t)P.nx * P.ny * P.n_cols;
+  float *dptr = P.out + ((size_t)y * P.nx + x) * P.n_cols + col + (long long)(kfirst - 2) * (long long)plane_floats;
+  const size_t drow = (size_t)P.nx * P.n_cols;
+  ClassColumn cf_col, ca_col;
+  cf_col.init(P.pcls_f, x, y, P.nx, P.ny, P.nz, P.pnx, P.pny, 0x01010101u * (unsigned)P.ncls_f);
+  ca_col.init(P.pcls_a, x, y, P.nx, P.ny, P.nz, P.pnx, P.pny, 0x01010101u * (unsigned)P.ncls_a);
+  // own rows of C(k-1) and T(k-2), the rows of T and D under way, and the z+ coefficients they still need
+  float4 cprev[4], tprev[4], accT[4], accD[4], rprev[kRing], accR[kRing];
+  float czpT[4], czpD[4], czpR[kRing];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    cprev[j] = zero4(); tprev[j] = zero4(); accT[j] = zero4(); accD[j] = zero4();
+    czpT[j] = 0.f; czpD[j] = 0.f;
+  }
+  unsigned wr[kRing];
+#pragma unroll
+  for (int r = 0; r < kRing; ++r) {
+    rprev[r] = zero4(); accR[r] = zero4(); czpR[r] = 0.f;
+    wr[r] = ring ? cr_col[r].at(kfirst) : 0u;
+  }
+  unsigned wf = cf_col.at(kfirst);
+  unsigned wa = ca_col.zero_word;  // classes of the second operator's rows of plane k - 1
+
+  for (int step = 0; step < steps; ++step) {
     const int k = kfirst + step;
-    const unsigned stage = n_use % kMarchStages;
-    const bool ok = mbar_wait(&S.full[stage], (n_use / kMarchStages) & 1u, P.wait_limit);
-    const char *cb = S.cbuf + stage * kMarchCBytes;
-    float4 own[PX * PY], nb[2 * PX + 2 * PY];
-    load_own<PX, PY, PC>(cb, xoC, yoC, own);
-    load_nb<PX, PY, PC>(cb, xoC, yoC, nb);
-    const unsigned wf_next = class_word(P.pcls_f, x, y, k + 1, P.nx, P.ny, P.nz, P.pnx, P.pny, zero_f);
-    char *tb = S.tbuf + ((k - 1) & 1) * kMarchTBytes;
+    const unsigned stage = cs.n_use % kMarchStages;
+    if (!wait_or_abort(S.full + 8 * stage, (cs.n_use / kMarchStages) & 1u, P.wait_limit, S.abort)) return false;
+    const unsigned cb = S.cbuf + stage * kMarchCBytes;
+    float4 own[4], nb[8], tcur[4], rown[kRing], rnb[kRing][4];
+    load_own<PC>(cb, xoC, yoC, own);
+    load_nb<PC>(cb, xoC, yoC, nb);
+    if (ring) {
+#pragma unroll
+      for (int r = 0; r < kRing; ++r) {
+        rown[r] = lds4(cb, roC[r]);
+        rnb[r][0] = lds4(cb, roC[r] - PC * 64);
+        rnb[r][1] = lds4(cb, roL[r]);
+        rnb[r][2] = lds4(cb, roR[r]);
+        rnb[r][3] = lds4(cb, roC[r] + PC * 64);
+      }
+    }
+    // T(k-1) is complete with its z+ product
+    const unsigned tb = S.tbuf + ((k - 1) & 1) * kMarchTBytes;
     const float *halo = (k - 1 == -1) ? P.t_lo : ((k - 1 == P.nz) ? P.t_hi : nullptr);
 #pragma unroll
-    for (int b = 0; b < PY; ++b)
+    for (int j = 0; j < 4; ++j) {
+      tcur[j] = fma4(czpT[j], own[j], accT[j]);
+      if (halo) tcur[j] = halo_row(halo, x + (j & 1), y + (j >> 1), col, P);
+      // (the buffer of T(k-1) was last read in step k-2; this thread has waited for every warp's arrival of
+      // step k-1, which each warp gives after its reads of step k-2)
+      sts4(tb, yoT + (j >> 1) * (PT * 64) + xoT[(j & 1) + 1], tcur[j]);
+    }
+    if (ring) {
 #pragma unroll
-      for (int a = 0; a < PX; ++a) {
-        const int j = b * PX + a;
-        float4 t = fma4(czp[j], own[j], accT[j]);
-        if (halo) {
-          const int gx = x + a, gy = y + b, col = c0col + 4 * c4;
-          t = zero4();
-          if (gx >= 0 && gx < P.nx && gy >= 0 && gy < P.ny && col < P.n_cols)
-            t = __ldg(reinterpret_cast<const float4 *>(halo + ((size_t)gy * P.nx + gx) * P.n_cols + col));
-        }
-        sts4(tb, yoT + b * (PT * 64) + xoT[a + 1], t);
+      for (int r = 0; r < kRing; ++r) {
+        float4 t = fma4(czpR[r], rown[r], accR[r]);
+        if (halo) t = halo_row(halo, rx[r], ry[r], col, P);
+        sts4(tb, roT[r], t);
       }
-    if (k >= zs - 1 && k <= ze) {
-      Coef cf[PX * PY];
-      patch_coefs<PX, PY>(cf, wf, x, y, S.dict_f, cF0);
-      stencil_partial<PX, PY>(accT, cprev, own, nb, cf);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(S.tbar);
+    // The class words of the next step are fetched only now: the arrive above is a release, which waits
+    // for every load the thread has in flight, and a load from global memory can take a microsecond.
+    const unsigned wf_next = cf_col.at(k + 1), wa_next = ca_col.at(k);
+    unsigned wr_next[kRing];
 #pragma unroll
-      for (int j = 0; j < PX * PY; ++j) czp[j] = cf[j].zp;
+    for (int r = 0; r < kRing; ++r) wr_next[r] = ring ? cr_col[r].at(k + 1) : 0u;
+    // D(k-2) is complete with its z+ product
+    if (k - 2 >= zs && k - 2 < ze) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 d = fma4(czpD[j], tcur[j], accD[j]);
+        if (live >> j & 1u) *reinterpret_cast<float4 *>(dptr + (j & 1) * (size_t)P.n_cols + (j >> 1) * drow) = d;
+      }
+    }
+    // T(k): everything but the z+ product
+    if (k >= zs - 1 && k <= ze) {
+      patch_start(accT, czpT, S.dict_f, wf, cprev, own, nb);
+      if (ring) {
+#pragma unroll
+        for (int r = 0; r < kRing; ++r)
+          czpR[r] = row_start(accR[r], S.dict_f, (wr[r] >> rsh[r]) & 255u, rprev[r], rnb[r][0], rnb[r][1], rown[r], rnb[r][2],
+                              rnb[r][3]);
+      }
     }
 #pragma unroll
-    for (int j = 0; j < PX * PY; ++j) cprev[j] = own[j];
+    for (int j = 0; j < 4; ++j) cprev[j] = own[j];
+#pragma unroll
+    for (int r = 0; r < kRing; ++r) { rprev[r] = rown[r]; wr[r] = wr_next[r]; }
     wf = wf_next;
-    if (__syncthreads_or(!ok)) return false;
+    // every warp has stored its rows of T(k-1) and is done with the plane C(k)
+    if (!wait_or_abort(S.tbar, cs.n_use & 1u, P.wait_limit, S.abort)) return false;
+    if (step + kMarchStages < steps) {
+      ++cs.n_iss;
+      if (tid == 0) {
+        mbar_expect_tx(S.full + 8 * stage, kMarchCBytes);
+        tma_load_plane(S.cbuf + stage * kMarchCBytes, tm_c, c0col, x0 / 2 - 1, y0 - 2, k + kMarchStages + P.z_shift, S.full + 8 * stage);
+      }
+    }
+    // D(k-1): everything but the z+ product, from T(k-2) (registers), T(k-1) (registers and neighbours)
+    if (k - 1 >= zs && k - 1 < ze) {
+      float4 tn[8];
+      load_nb<PT>(tb, xoT, yoT, tn);
+      patch_start(accD, czpD, S.dict_a, wa, tprev, tcur, tn);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) tprev[j] = tcur[j];
+    wa = wa_next;
+    ++cs.n_use;
+    dptr += plane_floats;
   }
   return true;
 }
 
 }  // namespace
 
-__global__ void __launch_bounds__(kMarchThreads, 1)
+__global__ void __launch_bounds__(kMarchThreads, kMarchCtasPerSm)
 lattice_march_kernel(const __grid_constant__ CUtensorMap tm_c, const MarchParams P) {
   extern __shared__ char dyn[];
   __shared__ int ctl[2];
-  char *sm = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~(uintptr_t)1023);
   Shared S;
-  S.cbuf = sm;
-  S.tbuf = sm + kMarchStages * kMarchCBytes;
-  S.dict_f = reinterpret_cast<float4 *>(S.tbuf + 2 * kMarchTBytes);
-  S.dict_a = S.dict_f + 2 * (kMarchMaxClassesDev + 1);
-  S.full = reinterpret_cast<unsigned long long *>(S.dict_a + 2 * (kMarchMaxClassesDev + 1));
+  S.cbuf = (smem_u32(dyn) + 1023u) & ~1023u;
+  S.tbuf = S.cbuf + kMarchStages * kMarchCBytes;
+  S.dict_f = S.tbuf + 2 * kMarchTBytes;
+  S.dict_a = S.dict_f + 32 * (kMarchMaxClassesDev + 1);
+  S.full = S.dict_a + 32 * (kMarchMaxClassesDev + 1);
+  S.tbar = S.full + 8 * kMarchStages;
+  S.abort = &ctl[1];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  for (int i = tid; i < 2 * (P.ncls_f + 1); i += kMarchThreads) S.dict_f[i] = __ldg(P.dict_f + i);
-  for (int i = tid; i < 2 * (P.ncls_a + 1); i += kMarchThreads) S.dict_a[i] = __ldg(P.dict_a + i);
+  for (int i = tid; i < 2 * (P.ncls_f + 1); i += kMarchThreads) sts4(S.dict_f, 16 * i, __ldg(P.dict_f + i));
+  for (int i = tid; i < 2 * (P.ncls_a + 1); i += kMarchThreads) sts4(S.dict_a, 16 * i, __ldg(P.dict_a + i));
   if (tid == 0) {
-    for (int s = 0; s < kMarchStages; ++s) mbar_init(&S.full[s], 1);
+    for (int s = 0; s < kMarchStages; ++s) mbar_init(S.full + 8 * s, 1);
+    mbar_init(S.tbar, kMarchThreads / 32);
+    ctl[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  const Coef cF0 = coef_from(S.dict_f[0], S.dict_f[1]);
-  const Coef cA0 = coef_from(S.dict_a[0], S.dict_a[1]);
-  const unsigned zero_f = 0x01010101u * (unsigned)P.ncls_f, zero_a = 0x01010101u * (unsigned)P.ncls_a;
 
-  // lane -> patch: four lanes (16 columns) per patch; the two patches of a quarter-warp are neighbours in x
-  const int c4 = lane & 3;
+  // lane -> patch: four lanes (16 columns) per patch; the two patches of a quarter-warp are neighbours in x.
+  // Warp w owns the patches of the tile's rows 2w, 2w + 1.
   const int pi = lane >> 2;  // 0 .. 7
+  // Ring rows of the group, relative to the tile origin.  In every load the two groups of a quarter-warp must
+  // read addresses an odd multiple of 64 bytes apart: two columns apart below / above the tile, the left and
+  // the right row of one y otherwise.
+  int rdx[kRing], rdy[kRing];
+  bool ring = true;
+  if (H == 16) {  // 64 rows, one per group: warps 0-3 below / above, warps 4-7 left / right
+    if (warp < 4) { rdx[0] = 8 * (warp & 1) + 2 * (pi & 3) + (pi >> 2); rdy[0] = warp < 2 ? -1 : H; }
+    else { rdx[0] = (pi & 1) ? W : -1; rdy[0] = 4 * (warp - 4) + (pi >> 1); }
+  } else {        // 48 rows, two per group of warps 0-2: below, above, left / right
+#pragma unroll
+    for (int r = 0; r < kRing; ++r) {
+      if (warp < 2) { rdx[r] = 2 * pi + r; rdy[r] = warp == 0 ? -1 : H; }
+      else { rdx[r] = (pi & 1) ? W : -1; rdy[r] = 2 * (pi >> 1) + r; }
+    }
+    ring = warp < 3;
+  }
 
-  unsigned n_use = 0;  // plane loads consumed by this CTA so far: stage = n_use % stages, parity from n_use / stages
-  unsigned n_iss = 0;  // plane loads issued so far (kept by the main warps; thread 0 issues them)
+  CtaState cs{0u, 0u};
   bool failed = false;
   for (;;) {
     if (tid == 0) ctl[0] = atomicAdd(&P.st->ticket, 1);
     __syncthreads();
     const int it = P.item_begin + ctl[0];
-    if (it >= P.item_end) break;
+    if (it >= P.item_end || ctl[1]) break;
     const int4 ia = __ldg(P.items + 2 * it), ib = __ldg(P.items + 2 * it + 1);
     const int x0 = ia.x, y0 = ia.y, zs = ia.z, ze = ia.w, c0col = ib.x;
     const int kfirst = zs - 2, steps = ze - zs + 4;
     if (tid == 0) {
       for (int s = 0; s < min(kMarchStages, steps); ++s) {
-        const unsigned stage = (n_use + s) % kMarchStages;
-        mbar_expect_tx(&S.full[stage], kMarchCBytes);
-        tma_load_plane(S.cbuf + stage * kMarchCBytes, &tm_c, c0col, x0 / 2 - 1, y0 - 2, kfirst + s + P.z_shift, &S.full[stage]);
+        const unsigned stage = (cs.n_use + s) % kMarchStages;
+        mbar_expect_tx(S.full + 8 * stage, kMarchCBytes);
+        tma_load_plane(S.cbuf + stage * kMarchCBytes, &tm_c, c0col, x0 / 2 - 1, y0 - 2, kfirst + s + P.z_shift, S.full + 8 * stage);
       }
     }
-    n_iss = n_use + min(kMarchStages, steps);
-    if (warp >= 8) {
-      // border ring of T: warps 8, 9 the rows below / above the tile, warps 10, 11 the columns left / right
-      bool ok;
-      // (the two groups of a quarter-warp take the left and the right strip of the same rows: their addresses
-      // differ by an odd multiple of 64 bytes in both rectangles)
-      if (warp == 8) ok = march_border<2, 1>(P, S, x0 + 2 * pi, y0 - 1, x0, y0, kfirst, steps, c0col, c4, n_use, cF0);
-      else if (warp == 9) ok = march_border<2, 1>(P, S, x0 + 2 * pi, y0 + H, x0, y0, kfirst, steps, c0col, c4, n_use, cF0);
-      else ok = march_border<1, 2>(P, S, (pi & 1) ? x0 + W : x0 - 1, y0 + 2 * (4 * (warp - 10) + (pi >> 1)), x0, y0, kfirst,
-                                   steps, c0col, c4, n_use, cF0);
-      if (!ok) { failed = true; break; }
-      continue;
-    }
-
-    // ---- main warps: 2 x 2 patches of the tile, both products ----
-    const int x = x0 + 2 * pi, y = y0 + 2 * warp;
-    int xoC[4], xoT[4];
+    cs.n_iss = cs.n_use + min(kMarchStages, steps);
+    int rx[kRing], ry[kRing];
 #pragma unroll
-    for (int a = -1; a <= 2; ++a) {
-      xoC[a + 1] = xoff<PC>(x - x0 + 2 + a) + c4 * 16;
-      xoT[a + 1] = xoff<PT>(x - x0 + 1 + a) + c4 * 16;
-    }
-    const int yoC = (y - y0 + 2) * (PC * 64), yoT = (y - y0 + 1) * (PT * 64);
-    const int col = c0col + 4 * c4;
-    const bool col_ok = col < P.n_cols;
-    float4 cprev[4], accT[4], tprev[4], accD[4];
-    float czpT[4], czpD[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      cprev[j] = zero4(); accT[j] = zero4(); tprev[j] = zero4(); accD[j] = zero4();
-      czpT[j] = 0.f; czpD[j] = 0.f;
-    }
-    unsigned wf = class_word(P.pcls_f, x, y, kfirst, P.nx, P.ny, P.nz, P.pnx, P.pny, zero_f);
-    unsigned wa = zero_a;  // classes of the second operator's rows of plane k - 1
-    bool ok_all = true;
-    for (int step = 0; step < steps; ++step, ++n_use) {
-      const int k = kfirst + step;
-      const unsigned stage = n_use % kMarchStages;
-      const bool ok = mbar_wait(&S.full[stage], (n_use / kMarchStages) & 1u, P.wait_limit);
-      const char *cb = S.cbuf + stage * kMarchCBytes;
-      float4 own[4], tcur[4];
-      {
-        float4 nb[8];
-        load_own<2, 2, PC>(cb, xoC, yoC, own);
-        load_nb<2, 2, PC>(cb, xoC, yoC, nb);
-        const unsigned wf_next = class_word(P.pcls_f, x, y, k + 1, P.nx, P.ny, P.nz, P.pnx, P.pny, zero_f);
-        const unsigned wa_next = class_word(P.pcls_a, x, y, k, P.nx, P.ny, P.nz, P.pnx, P.pny, zero_a);
-        // T(k-1) is complete with its z+ product
-        char *tb = S.tbuf + ((k - 1) & 1) * kMarchTBytes;
-        const float *halo = (k - 1 == -1) ? P.t_lo : ((k - 1 == P.nz) ? P.t_hi : nullptr);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          tcur[j] = fma4(czpT[j], own[j], accT[j]);
-          if (halo) {
-            const int gx = x + (j & 1), gy = y + (j >> 1);
-            tcur[j] = zero4();
-            if (gx < P.nx && gy < P.ny && col_ok)
-              tcur[j] = __ldg(reinterpret_cast<const float4 *>(halo + ((size_t)gy * P.nx + gx) * P.n_cols + col));
-          }
-          sts4(tb, yoT + (j >> 1) * (PT * 64) + xoT[(j & 1) + 1], tcur[j]);
-        }
-        // D(k-2) is complete with its z+ product
-        if (k - 2 >= zs && k - 2 < ze) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float4 d = fma4(czpD[j], tcur[j], accD[j]);
-            const int gx = x + (j & 1), gy = y + (j >> 1);
-            if (gx < P.nx && gy < P.ny && col_ok)
-              *reinterpret_cast<float4 *>(P.out + (((size_t)(k - 2) * P.ny + gy) * P.nx + gx) * P.n_cols + col) = d;
-          }
-        }
-        // T(k): everything but the z+ product
-        if (k >= zs - 1 && k <= ze) {
-          Coef cf[4];
-          patch_coefs<2, 2>(cf, wf, x, y, S.dict_f, cF0);
-          stencil_partial<2, 2>(accT, cprev, own, nb, cf);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) czpT[j] = cf[j].zp;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) cprev[j] = own[j];
-        wf = wf_next;
-        // wa still holds the classes of plane k - 1 for the D(k-1) start below; wa_next those of plane k
-        if (__syncthreads_or(!ok)) { ok_all = false; break; }
-        if (step + kMarchStages < steps) {
-          ++n_iss;
-          if (tid == 0) {
-            mbar_expect_tx(&S.full[stage], kMarchCBytes);
-            tma_load_plane(S.cbuf + stage * kMarchCBytes, &tm_c, c0col, x0 / 2 - 1, y0 - 2, k + kMarchStages + P.z_shift, &S.full[stage]);
-          }
-        }
-        // D(k-1): everything but the z+ product, from T(k-2) (registers), T(k-1) (registers and neighbours)
-        if (k - 1 >= zs && k - 1 < ze) {
-          float4 tn[8];
-          load_nb<2, 2, PT>(tb, xoT, yoT, tn);
-          Coef ca[4];
-          patch_coefs<2, 2>(ca, wa, x, y, S.dict_a, cA0);
-          stencil_partial<2, 2>(accD, tprev, tcur, tn, ca);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) czpD[j] = ca[j].zp;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) tprev[j] = tcur[j];
-        wa = wa_next;
-      }
-    }
-    if (!ok_all) { failed = true; break; }
+    for (int r = 0; r < kRing; ++r) { rx[r] = x0 + rdx[r]; ry[r] = y0 + rdy[r]; }
+    if (!run_item(&tm_c, P, S, cs, x0, y0, zs, ze, c0col, x0 + 2 * pi, y0 + 2 * warp, ring, rx, ry)) { failed = true; break; }
   }
-  if (failed) {
-    // Leave together: every thread of the CTA saw the same abort vote.  Copies still in flight must land
-    // before the shared memory is given up; thread 0 waits for each stage it armed, again with a limit.
-    if (tid == 0) {
-      atomicExch(&P.st->error, 1);
-      for (unsigned q = n_use; q != n_iss; ++q)
-        mbar_wait(&S.full[q % kMarchStages], (q / kMarchStages) & 1u, P.wait_limit);
-    }
-  }
+  if (failed && tid == 0) atomicExch(&P.st->error, 1);
+  // A thread that gave up has raised the CTA's abort flag; the others notice it in their own bounded waits
+  // and arrive here too.  Copies still in flight must land before the shared memory is given up: thread 0
+  // waits for each stage it armed, again with a limit.
   __syncthreads();
+  if (ctl[1] && tid == 0) {
+    atomicExch(&P.st->error, 1);
+    for (unsigned q = cs.n_use; q != cs.n_iss; ++q) mbar_wait(S.full + 8 * (q % kMarchStages), (q / kMarchStages) & 1u, P.wait_limit);
+  }
   if (tid == 0) {
     __threadfence();
     const int f = atomicAdd(&P.st->finished, 1);
@@ -427,14 +459,23 @@ int march_make_map(CUtensorMap *out, const float *c, int n_cols, int nx, int ny,
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// CTAs of the kernel that fit one SM (0 on error).  The first call also raises the kernel's shared-memory limits.
+int march_ctas_per_sm() {
+  static int occ = -1;
+  if (occ >= 0) return occ;
+  const void *fn = (const void *)lattice_march_kernel;
+  if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMarchSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+    return 0;
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lattice_march_kernel, kMarchThreads, kMarchSmemBytes) != cudaSuccess)
+    return 0;
+  occ = n;
+  return occ;
+}
+
 cudaError_t launch_lattice_march(int grid, const CUtensorMap &tm_c, const MarchParams &p, cudaStream_t s) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute((const void *)lattice_march_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kMarchSmemBytes);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+  if (march_ctas_per_sm() <= 0) return cudaErrorLaunchOutOfResources;
   lattice_march_kernel<<<grid, kMarchThreads, kMarchSmemBytes, s>>>(tm_c, p);
   return cudaGetLastError();
 }

@@ -6,10 +6,11 @@
 
 namespace tfk {
 
-constexpr int kMarchW = 16, kMarchH = 16;   // grid points of a tile in x and y
+constexpr int kMarchW = 16, kMarchH = 8;    // grid points of a tile in x and y
 constexpr int kMarchCols = 16;              // dense columns per chunk (64 bytes per row)
 constexpr int kMarchStages = 4;             // planes of C in flight per CTA
-constexpr int kMarchThreads = 384;          // 8 warps of 2 x 2 patches + 4 warps for the border ring of T
+constexpr int kMarchThreads = 128;          // 4 warps: 32 patches of 2 x 2 grid points x 4 lanes of 4 columns
+constexpr int kMarchCtasPerSm = 2;          // two independent CTAs per SM: one loads while the other computes
 constexpr int kMarchCBytes = (kMarchW + 4) * (kMarchH + 4) * kMarchCols * 4;                          // 25 600
 constexpr int kMarchTBytes = ((kMarchW + 2) * (kMarchH + 2) * kMarchCols * 4 + 1023) / 1024 * 1024;  // 21 504
 constexpr int kMarchMaxClassesDev = 63;
@@ -39,6 +40,7 @@ struct MarchParams {
 
 // Tensor map of C as a 5-D fp32 tensor (n_cols, nx / 2, 2, ny, planes), box = 16 columns x (W+4)/2 x 2 x (H+4) x 1.
 int march_make_map(CUtensorMap *out, const float *c, int n_cols, int nx, int ny, long long planes);
+int march_ctas_per_sm();
 cudaError_t launch_lattice_march(int grid, const CUtensorMap &tm_c, const MarchParams &p, cudaStream_t s);
 
 }  // namespace tfk
