@@ -257,18 +257,12 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     const unsigned stage = cs.n_use % kMarchStages;
     if (!wait_or_abort(S.full + 8 * stage, (cs.n_use / kMarchStages) & 1u, P.wait_limit, S.abort)) return false;
     const unsigned cb = S.cbuf + stage * kMarchCBytes;
-    float4 own[4], nb[8], tcur[4], rown[kRing], rnb[kRing][4];
+    float4 own[4], nb[8], tcur[4], rown[kRing];
     load_own<PC>(cb, xoC, yoC, own);
     load_nb<PC>(cb, xoC, yoC, nb);
     if (ring) {
 #pragma unroll
-      for (int r = 0; r < kRing; ++r) {
-        rown[r] = lds4(cb, roC[r]);
-        rnb[r][0] = lds4(cb, roC[r] - PC * 64);
-        rnb[r][1] = lds4(cb, roL[r]);
-        rnb[r][2] = lds4(cb, roR[r]);
-        rnb[r][3] = lds4(cb, roC[r] + PC * 64);
-      }
+      for (int r = 0; r < kRing; ++r) rown[r] = lds4(cb, roC[r]);
     }
     // T(k-1) is complete with its z+ product
     const unsigned tb = S.tbuf + ((k - 1) & 1) * kMarchTBytes;
@@ -309,10 +303,14 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     if (k >= zs - 1 && k <= ze) {
       patch_start(accT, czpT, S.dict_f, wf, cprev, own, nb);
       if (ring) {
+        // (the ring rows' neighbours are read only now, when the patch's are no longer needed: the plane stays
+        // in its stage until every warp has passed the wait below)
 #pragma unroll
-        for (int r = 0; r < kRing; ++r)
-          czpR[r] = row_start(accR[r], S.dict_f, (wr[r] >> rsh[r]) & 255u, rprev[r], rnb[r][0], rnb[r][1], rown[r], rnb[r][2],
-                              rnb[r][3]);
+        for (int r = 0; r < kRing; ++r) {
+          const float4 ym = lds4(cb, roC[r] - PC * 64), xm = lds4(cb, roL[r]), xp = lds4(cb, roR[r]);
+          const float4 yp = lds4(cb, roC[r] + PC * 64);
+          czpR[r] = row_start(accR[r], S.dict_f, (wr[r] >> rsh[r]) & 255u, rprev[r], ym, xm, rown[r], xp, yp);
+        }
       }
     }
 #pragma unroll
