@@ -406,7 +406,7 @@ def main():
     achieved = bytes_local / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": None, "peak_source": f"of {peak_kind}", "algorithmic_bytes_per_launch": bytes_local,
-                "kernel": ("tile_pipeline_kernel" if plan.info()["threads"] == 672 else "stream_kernel")
+                "kernel": {128: "lattice_march_kernel", 672: "tile_pipeline_kernel"}.get(plan.info()["threads"], "stream_kernel")
                           + " (persistent fused executor)", "kernel_ms": kernel_ms,
                 "kernel_ms_min": float(np.min(per_step))}
     if world == 1 and not args.dims and args.mode == "stream" and args.workload in DRAM_TRAFFIC:

@@ -28,9 +28,11 @@ def test_spmm_spmm_128cubed(built_lib):
     t = synth.laplacian(dims)
     A = api.CSRMatrix(n, n, *t)
     S = _scipy_csr(t, n)
-    plans = {"pipeline": api.Plan("spmm_spmm", A, n_cols=n_cols),
-             "two_cta_tiles": api.Plan("spmm_spmm", A, n_cols=n_cols, tile_pipeline=-1),
+    plans = {"march": api.Plan("spmm_spmm", A, n_cols=n_cols),
+             "pipeline": api.Plan("spmm_spmm", A, n_cols=n_cols, lattice_march=-1),
+             "two_cta_tiles": api.Plan("spmm_spmm", A, n_cols=n_cols, tile_pipeline=-1, lattice_march=-1),
              "unfused_direct": api.Plan("spmm_spmm", A, n_cols=n_cols, mode=api.MODE_UNFUSED, tile_slots=-1)}
+    assert plans["march"].info()["threads"] == 128      # the plane-marching kernel: the intermediate stays on chip
     assert plans["pipeline"].info()["threads"] == 672
     c = torch.empty((n, n_cols), device="cuda")
     _fill(torch, c, 3)
@@ -41,17 +43,18 @@ def test_spmm_spmm_128cubed(built_lib):
         p.status()
         out[name] = d
     # every mode adds the same products in the same order
+    assert torch.equal(out["march"], out["unfused_direct"])
     assert torch.equal(out["pipeline"], out["unfused_direct"])
     assert torch.equal(out["two_cta_tiles"], out["unfused_direct"])
     # single columns against fp64
-    d = out["pipeline"]
+    d = out["march"]
     for j in (0, 77, 127):
         cj = c[:, j].double().cpu().numpy()
         common.assert_close(d[:, j].cpu().numpy(), S @ (S @ cj), f"column {j}")
     # constant operand: every product and sum is a small integer, so the result is exact
     c.fill_(1.0)
-    plans["pipeline"].spmm_spmm(c, d)
-    plans["pipeline"].status()
+    plans["march"].spmm_spmm(c, d)
+    plans["march"].status()
     want = S @ (S @ np.ones(n))
     assert np.array_equal(d[:, 5].cpu().numpy().astype(np.float64), want)
     assert torch.equal(d, d[:, :1].expand(-1, n_cols))
@@ -60,7 +63,7 @@ def test_spmm_spmm_128cubed(built_lib):
     _fill(torch, x, 11)
     _fill(torch, y, 12)
     dx, dy, dz = torch.empty_like(c), torch.empty_like(c), torch.empty_like(c)
-    p = plans["pipeline"]
+    p = plans["march"]
     p.spmm_spmm(x, dx)
     p.spmm_spmm(y, dy)
     p.spmm_spmm(x + 2 * y, dz)

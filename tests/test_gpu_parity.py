@@ -68,7 +68,8 @@ def test_spmm_spmm_all_modes(torch_cuda, oracle, mat, n_cols):
     variants = [("stream_ring", dict(mode=api.MODE_STREAM, rows_per_block=16, slack_blocks=4, ring_bytes=1 << 30,
                                      tile_slots=-1)),
                 ("stream_default", dict(mode=api.MODE_STREAM)),
-                ("stream_two_cta_tiles", dict(mode=api.MODE_STREAM, tile_pipeline=-1)),
+                ("stream_tile_pipeline", dict(mode=api.MODE_STREAM, lattice_march=-1)),
+                ("stream_two_cta_tiles", dict(mode=api.MODE_STREAM, tile_pipeline=-1, lattice_march=-1)),
                 ("stream_noring", dict(mode=api.MODE_STREAM, ring_bytes=-1, rows_per_block=8, tile_slots=-1)),
                 ("tiled_ring", dict(mode=api.MODE_STREAM, tile_slots=160, tile_max_bz=2, ring_bytes=1 << 30,
                                     slack_blocks=3)),
@@ -84,7 +85,9 @@ def test_spmm_spmm_all_modes(torch_cuda, oracle, mat, n_cols):
         plan.status()
         results[name] = d.cpu().numpy()
         common.assert_close(results[name], want, f"{mat} N={n_cols} {name}")
-        if name == "stream_default" and mat.startswith("lap") and n_cols % 4 == 0:
+        if name == "stream_default" and mat == "lap3d_14" and n_cols % 4 == 0:
+            assert plan.info()["threads"] == 128, plan.info()  # star stencil on a 3-D grid: the plane-marching kernel
+        if name == "stream_tile_pipeline" and mat.startswith("lap") and n_cols % 4 == 0:
             assert plan.info()["threads"] == 672, plan.info()  # both operators tiled: the tile pipeline runs it
         if name == "stream_two_cta_tiles" and mat.startswith("lap") and n_cols % 4 == 0:
             assert plan.info()["threads"] == 512, plan.info()
@@ -100,6 +103,46 @@ def test_spmm_spmm_all_modes(torch_cuda, oracle, mat, n_cols):
     if mat.startswith("lap"):
         for name in results:
             np.testing.assert_array_equal(results[name], results["unfused"], err_msg=name)
+
+
+@pytest.mark.parametrize("dims,n_cols", [((40, 34, 9), 100), ((18, 16, 5), 128), ((16, 8, 3), 4), ((34, 20, 20), 48)])
+def test_plane_march_shapes(torch_cuda, oracle, dims, n_cols):
+    """The plane-marching kernel on grids that are no multiples of its 16 x 8 tiles, widths that are no multiples
+    of its 16-column chunks, and two different operators: against the oracle's two CSR products, and bit for
+    bit against the unfused CSR executor."""
+    torch = torch_cuda
+    a = synth.laplacian(dims)
+    n = len(a[0]) - 1
+    rows = np.repeat(np.arange(n), np.diff(a[0]))
+    bx = (a[2] * (1.0 + (rows % 2)) * np.where(a[1] > rows, 0.5, 1.0)).astype(np.float32)
+    b = (a[0], a[1], bx)
+    c = synth.uniform(3, (n, n_cols))
+    cd = _dev(torch, c)
+    for first, what in ((a, "B = A"), (b, "B != A")):
+        A, B = _csr(a), _csr(first)
+        want = oracle.spmm(a[0], a[1], a[2], oracle.spmm(first[0], first[1], first[2], c))
+        plan = api.Plan("spmm_spmm", A, B=None if first is a else B, n_cols=n_cols)
+        assert plan.info()["threads"] == 128, plan.info()
+        d = torch.full((n, n_cols), float("nan"), device="cuda")
+        for _ in range(2):
+            plan.spmm_spmm(cd, d)
+        plan.status()
+        common.assert_close(d.cpu().numpy(), want, f"plane march {dims} N={n_cols} {what}")
+        ref_plan = api.Plan("spmm_spmm", A, B=None if first is a else B, n_cols=n_cols, mode=api.MODE_UNFUSED, tile_slots=-1,
+                            lattice_march=-1)
+        d0 = torch.empty_like(d)
+        ref_plan.spmm_spmm(cd, d0)
+        ref_plan.status()
+        assert torch.equal(d, d0), what
+        # an operand that is not 16-byte aligned takes the general path of the same plan
+        c1 = torch.empty(n * n_cols + 1, device="cuda")[1:].view(n, n_cols)
+        c1.copy_(cd)
+        d1 = torch.empty_like(d)
+        plan.spmm_spmm(c1, d1)
+        plan.status()
+        assert torch.equal(d1, d0), what + ", unaligned operand"
+        plan.close()
+        ref_plan.close()
 
 
 def test_spmm_spmm_two_operators_and_host_path(torch_cuda, oracle):

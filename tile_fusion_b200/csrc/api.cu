@@ -137,7 +137,7 @@ struct tf_plan {
   int tile_info[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // producer bx,by,bz,tiles ; consumer bx,by,bz,tiles
   // plane-marching executor (both operators are star stencils on one grid)
   struct March {
-    bool on = false;
+    bool on = false, same = false;  // same: one operator on both sides (B == A)
     int nx = 0, ny = 0, nz = 0, ncls_f = 0, ncls_a = 0, z_shift = 0, grid = 0, n_items = 0;
     long long planes_c = 0;
     DevBuf<unsigned> pcls_f, pcls_a;
@@ -329,8 +329,9 @@ int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int sm_count) {
   rc = M.items.upload(raw);
   if (rc == TF_OK) rc = M.pcls_f.upload(lf.patch_cls);
   if (rc == TF_OK) rc = M.dict_f.upload(lf.dict);
-  if (rc == TF_OK) rc = M.pcls_a.upload(la.patch_cls);
-  if (rc == TF_OK) rc = M.dict_a.upload(la.dict);
+  M.same = &F == &A;
+  if (rc == TF_OK && !M.same) rc = M.pcls_a.upload(la.patch_cls);
+  if (rc == TF_OK && !M.same) rc = M.dict_a.upload(la.dict);
   if (rc == TF_OK) rc = M.st.alloc(1);
   if (rc != TF_OK) return rc;
   TF_CUDA(cudaMemset(M.st.p, 0, sizeof(tfk::MarchState)));
@@ -348,9 +349,9 @@ int run_march(tf_plan &p, const float *C, float *D, int item_begin, int item_end
   if (mr != 0) return fail(TF_ERR_CUDA, "cuTensorMapEncodeTiled failed for the dense operand (code " + std::to_string(mr) + ")");
   tfk::MarchParams Q;
   std::memset(&Q, 0, sizeof(Q));
-  Q.pcls_f = M.pcls_f.p; Q.pcls_a = M.pcls_a.p;
+  Q.pcls_f = M.pcls_f.p; Q.pcls_a = M.same ? M.pcls_f.p : M.pcls_a.p;
   Q.dict_f = reinterpret_cast<const float4 *>(M.dict_f.p);
-  Q.dict_a = reinterpret_cast<const float4 *>(M.dict_a.p);
+  Q.dict_a = M.same ? Q.dict_f : reinterpret_cast<const float4 *>(M.dict_a.p);
   Q.ncls_f = M.ncls_f; Q.ncls_a = M.ncls_a;
   Q.out = D;
   Q.items = M.items.p;

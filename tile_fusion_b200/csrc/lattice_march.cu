@@ -303,8 +303,8 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     if (k >= zs - 1 && k <= ze) {
       patch_start(accT, czpT, S.dict_f, wf, cprev, own, nb);
       if (ring) {
-        // (the ring rows' neighbours are read only now, when the patch's are no longer needed: the plane stays
-        // in its stage until every warp has passed the wait below)
+        // (the ring rows' neighbours are read only now, when the patch's are no longer needed; the stage is
+        // refilled one step later, see below)
 #pragma unroll
         for (int r = 0; r < kRing; ++r) {
           const float4 ym = lds4(cb, roC[r] - PC * 64), xm = lds4(cb, roL[r]), xp = lds4(cb, roR[r]);
@@ -320,11 +320,15 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     wf = wf_next;
     // every warp has stored its rows of T(k-1) and is done with the plane C(k)
     if (!wait_or_abort(S.tbar, cs.n_use & 1u, P.wait_limit, S.abort)) return false;
-    if (step + kMarchStages < steps) {
+    // Every warp has therefore finished step k-1, ring rows included (those read their plane after the
+    // arrive): the stage of plane k-1 can take plane k-1 + stages.
+    if (step > 0 && step - 1 + kMarchStages < steps) {
       ++cs.n_iss;
       if (tid == 0) {
-        mbar_expect_tx(S.full + 8 * stage, kMarchCBytes);
-        tma_load_plane(S.cbuf + stage * kMarchCBytes, tm_c, c0col, x0 / 2 - 1, y0 - 2, k + kMarchStages + P.z_shift, S.full + 8 * stage);
+        const unsigned prev_stage = (cs.n_use - 1) % kMarchStages;
+        mbar_expect_tx(S.full + 8 * prev_stage, kMarchCBytes);
+        tma_load_plane(S.cbuf + prev_stage * kMarchCBytes, tm_c, c0col, x0 / 2 - 1, y0 - 2, k - 1 + kMarchStages + P.z_shift,
+                       S.full + 8 * prev_stage);
       }
     }
     // D(k-1): everything but the z+ product, from T(k-2) (registers), T(k-1) (registers and neighbours)
@@ -462,11 +466,10 @@ int march_ctas_per_sm() {
   static int occ = -1;
   if (occ >= 0) return occ;
   const void *fn = (const void *)lattice_march_kernel;
-  if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMarchSmemBytes) != cudaSuccess ||
-      cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
-    return 0;
   int n = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lattice_march_kernel, kMarchThreads, kMarchSmemBytes) != cudaSuccess)
+  if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMarchSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lattice_march_kernel, kMarchThreads, kMarchSmemBytes) != cudaSuccess)
     return 0;
   occ = n;
   return occ;
