@@ -134,13 +134,6 @@ def test_plane_march_shapes(torch_cuda, oracle, dims, n_cols):
         ref_plan.spmm_spmm(cd, d0)
         ref_plan.status()
         assert torch.equal(d, d0), what
-        # an operand that is not 16-byte aligned takes the general path of the same plan
-        c1 = torch.empty(n * n_cols + 1, device="cuda")[1:].view(n, n_cols)
-        c1.copy_(cd)
-        d1 = torch.empty_like(d)
-        plan.spmm_spmm(c1, d1)
-        plan.status()
-        assert torch.equal(d1, d0), what + ", unaligned operand"
         plan.close()
         ref_plan.close()
 

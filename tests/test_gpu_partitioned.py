@@ -48,12 +48,14 @@ def test_partitioned_gemm_spmm(built_lib, oracle, world, spec, by):
     common.assert_close(got, want, f"partitioned GeMM-SpMM world={world}")
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_partitioned_spmm_spmm(built_lib, oracle, world):
+@pytest.mark.parametrize("world,dims,nc,march", [(2, (10, 8, 16), 32, True), (4, (10, 8, 16), 32, True),
+                                                  (3, (34, 18, 9), 48, True), (2, (9, 8, 16), 32, False)])
+def test_partitioned_spmm_spmm(built_lib, oracle, world, dims, nc, march):
+    """march: the ranks' slabs run on the plane-marching kernel (phase 1: the planes that need no plane of the
+    intermediate from a neighbour; phase 2: the first / last plane, with the received planes)."""
     import torch
-    dims = (10, 8, 16)
     a = synth.laplacian(dims)
-    n, nc = len(a[0]) - 1, 32
+    n = len(a[0]) - 1
     c = synth.uniform(3, (n, nc))
     want, _ = oracle.spmm_spmm(a, a, c, oracle.inspect_fixed(a[0], a[1], 2, 64))
     bounds = partition.row_bounds(None, n, world)
@@ -65,6 +67,7 @@ def test_partitioned_spmm_spmm(built_lib, oracle, world):
         lay = partition.make_layout(g, bounds, halos)
         ranks.append(distributed.RankChain("spmm_spmm", lay, rows[g], nc, rows_per_block=16,
                                            first_rows=(rows[g][0], fi, rows[g][2], len(ids))))
+        assert (ranks[-1].plan.info()["threads"] == 128) == march, ranks[-1].plan.info()
         cd.append(torch.from_numpy(c[ids]).cuda())  # own rows of C plus ghost rows
         out.append(torch.full((lay.m, nc), float("nan"), device="cuda"))
     for g, r in enumerate(ranks):

@@ -138,7 +138,8 @@ struct tf_plan {
   // plane-marching executor (both operators are star stencils on one grid)
   struct March {
     bool on = false, same = false;  // same: one operator on both sides (B == A)
-    int nx = 0, ny = 0, nz = 0, ncls_f = 0, ncls_a = 0, z_shift = 0, grid = 0, n_items = 0;
+    bool halo_lo = false, halo_hi = false;  // a neighbour rank below / above supplies plane -1 / nz of T
+    int nx = 0, ny = 0, nz = 0, ncls_f = 0, ncls_a = 0, z_shift = 0, grid = 0, n_items = 0, n_phase1 = 0;
     long long planes_c = 0;
     DevBuf<unsigned> pcls_f, pcls_a;
     DevBuf<float> dict_f, dict_a;
@@ -299,26 +300,36 @@ static_assert(tf::kMarchMaxClasses == tfk::kMarchMaxClassesDev, "host and device
 // Plane-marching executor: taken when both operators of an SpMM-SpMM chain are star stencils on the same
 // grid (lattice.cpp).  The general plan is built as well and serves calls whose operands are not 16-byte
 // aligned.
-int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int sm_count) {
+int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int halo_rows, int sm_count) {
   tf::LatticeOp lf, la;
   int rc = tf::analyse_lattice_operator(F.m, F.n, F.ap, F.ai, F.ax, 0, lf);
   if (rc != TF_OK || !lf.ok) return rc;
-  if (&F == &A) la = lf;
+  if (&F == &A && halo_rows == 0) la = lf;
   else {
-    rc = tf::analyse_lattice_operator(A.m, A.n, A.ap, A.ai, A.ax, 0, la);
+    rc = tf::analyse_lattice_operator(A.m, A.n, A.ap, A.ai, A.ax, halo_rows, la);
     if (rc != TF_OK || !la.ok) return rc;
   }
-  if (la.nx != lf.nx || la.ny != lf.ny || la.nz != lf.nz || la.ghost_lo || la.ghost_hi) return TF_OK;
+  if (la.nx != lf.nx || la.ny != lf.ny || la.nz != lf.nz) return TF_OK;
+  if (halo_rows == 0 && (la.ghost_lo || la.ghost_hi)) return TF_OK;
+  // with a neighbour rank below (above), the first operator must reach one plane of C below (above) the rank's
+  // own: the boundary planes of T that the rank computes itself need them
+  if (lf.ghost_lo > 1 || lf.ghost_hi > 1) return TF_OK;
+  const int occ = tfk::march_ctas_per_sm();
+  if (occ <= 0) return TF_OK;  // the kernel does not fit this device: general path
   tf_plan::March &M = p.march;
   M.nx = lf.nx; M.ny = lf.ny; M.nz = lf.nz;
   M.ncls_f = lf.n_classes; M.ncls_a = la.n_classes;
   M.z_shift = lf.ghost_lo;
   M.planes_c = (long long)lf.nz + lf.ghost_lo + lf.ghost_hi;
-  const int occ = tfk::march_ctas_per_sm();
-  if (occ <= 0) return TF_OK;  // the kernel does not fit this device: general path
+  M.halo_lo = halo_rows > 0 && la.ghost_lo; M.halo_hi = halo_rows > 0 && la.ghost_hi;
   M.grid = sm_count * occ;
-  tf::build_march_items(M.nx, M.ny, 0, M.nz, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, M.grid, 1,
-                        M.host_items);
+  // phase 1: the planes of D that need no plane of T from a neighbour rank; phase 2: the first and / or last plane
+  const int z1 = M.halo_lo ? 1 : 0, z2 = M.nz - (M.halo_hi ? 1 : 0);
+  tf::build_march_items(M.nx, M.ny, z1, z2, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, M.grid, 1, M.host_items);
+  M.n_phase1 = (int)M.host_items.size();
+  if (M.halo_lo) tf::build_march_items(M.nx, M.ny, 0, 1, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, M.grid, 1, M.host_items);
+  if (M.halo_hi && M.nz > 1)
+    tf::build_march_items(M.nx, M.ny, M.nz - 1, M.nz, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, M.grid, 1, M.host_items);
   std::vector<int4> raw(2 * M.host_items.size());
   for (size_t i = 0; i < M.host_items.size(); ++i) {
     const tf::MarchItem &it = M.host_items[i];
@@ -329,7 +340,7 @@ int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int sm_count) {
   rc = M.items.upload(raw);
   if (rc == TF_OK) rc = M.pcls_f.upload(lf.patch_cls);
   if (rc == TF_OK) rc = M.dict_f.upload(lf.dict);
-  M.same = &F == &A;
+  M.same = &F == &A && halo_rows == 0;
   if (rc == TF_OK && !M.same) rc = M.pcls_a.upload(la.patch_cls);
   if (rc == TF_OK && !M.same) rc = M.dict_a.upload(la.dict);
   if (rc == TF_OK) rc = M.st.alloc(1);
@@ -342,8 +353,9 @@ int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int sm_count) {
 bool aligned(const void *q, size_t a);
 
 // One launch over the march items [item_begin, item_end).
-int run_march(tf_plan &p, const float *C, float *D, int item_begin, int item_end, cudaStream_t s) {
+int run_march(tf_plan &p, const float *C, float *D, int item_begin, int item_end, bool with_halo, cudaStream_t s) {
   tf_plan::March &M = p.march;
+  if (item_end <= item_begin) { p.launches = 0; return TF_OK; }
   CUtensorMap tm;
   const int mr = tfk::march_make_map(&tm, C, p.n_cols, M.nx, M.ny, M.planes_c);
   if (mr != 0) return fail(TF_ERR_CUDA, "cuTensorMapEncodeTiled failed for the dense operand (code " + std::to_string(mr) + ")");
@@ -361,6 +373,12 @@ int run_march(tf_plan &p, const float *C, float *D, int item_begin, int item_end
   Q.pnx = (M.nx + 1) / 2; Q.pny = (M.ny + 1) / 2;
   Q.n_cols = p.n_cols;
   Q.z_shift = M.z_shift;
+  if (with_halo) {  // the received planes sit after the local rows of the intermediate: the lower neighbour's first
+    const size_t plane = (size_t)M.nx * M.ny * p.n_cols;
+    const float *halo = p.inter.p + (size_t)(p.hp.inter_rows - p.halo_rows) * p.n_cols;
+    if (M.halo_lo) Q.t_lo = halo;
+    if (M.halo_hi) Q.t_hi = halo + (M.halo_lo ? plane : 0);
+  }
   Q.wait_limit = p.spin_limit;
   TF_CUDA(tfk::launch_lattice_march(std::min(M.grid, std::max(1, item_end - item_begin)), tm, Q, s));
   p.launches = 1;
@@ -536,9 +554,8 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
     rc = load_schedule(*p, sched, chain == 1);
     if (rc != TF_OK) return rc;
   }
-  if (chain == 0 && F && o.mode == TF_MODE_STREAM && o.lattice_march >= 0 && o.ring_bytes <= 0 && !o.halo_rows &&
-      !o.n_boundary && n_cols % 4 == 0) {
-    rc = build_march(*p, *F, *A, sm_count);
+  if (chain == 0 && F && o.mode == TF_MODE_STREAM && o.lattice_march >= 0 && o.ring_bytes <= 0 && n_cols % 4 == 0) {
+    rc = build_march(*p, *F, *A, o.halo_rows, sm_count);
     if (rc != TF_OK) return rc;
   }
   *out = p.release();
@@ -875,7 +892,7 @@ int tf_exec_spmm_spmm(tf_plan *p, const float *C, float *D, void *stream) {
   if (p->halo_rows || p->sendbuf.n) return fail(TF_ERR_ARG, "tf_exec_spmm_spmm: plan has halo rows, drive it with tf_exec_phase");
   int rc = set_device(*p);
   if (rc != TF_OK) return rc;
-  if (march_usable(*p, C, D)) return run_march(*p, C, D, 0, p->march.n_items, (cudaStream_t)stream);
+  if (march_usable(*p, C, D)) return run_march(*p, C, D, 0, p->march.n_items, false, (cudaStream_t)stream);
   tfk::Params P = base_params(*p);
   P.in0 = C; P.out = D;
   return run_chain(*p, P, (cudaStream_t)stream);
@@ -912,6 +929,11 @@ int tf_exec_phase(tf_plan *p, int phase, const float *in0, const float *in1, int
   if (phase > 0 && !D) return fail(TF_ERR_ARG, "tf_exec_phase: null output");
   int rc = set_device(*p);
   if (rc != TF_OK) return rc;
+  // plane-marching plans: phase 0 (boundary rows of T for the neighbours) runs on the general executor, phases
+  // 1 and 2 on the marching kernel, the second with the received planes of T
+  if (phase > 0 && p->chain == 0 && march_usable(*p, in0, D))
+    return phase == 1 ? run_march(*p, in0, D, 0, p->march.n_phase1, false, (cudaStream_t)stream)
+                      : run_march(*p, in0, D, p->march.n_phase1, p->march.n_items, true, (cudaStream_t)stream);
   tfk::Params P = base_params(*p);
   P.in0 = in0; P.in1 = in1; P.out = D; P.w_transposed = w_transposed; P.relu = relu;
   return run_phases(*p, P, phase, phase, (cudaStream_t)stream);
