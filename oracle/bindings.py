@@ -183,13 +183,29 @@ class Ref:
     """The unmodified reference compiled in place (oracle/_ref/libtf_ref.so)."""
 
     PATH = os.path.join(_HERE, "_ref", "libtf_ref.so")
+    PATH_AVX512 = os.path.join(_HERE, "_ref", "libtf_ref_avx512.so")
 
     @classmethod
     def available(cls) -> bool:
         return os.path.exists(cls.PATH)
 
-    def __init__(self, use_mkl_sgemm: bool = True):
-        L = self.lib = C.CDLL(self.PATH)
+    @classmethod
+    def avx512_available(cls) -> bool:
+        """The AVX-512 build exists and this host's CPU can run it."""
+        if not os.path.exists(cls.PATH_AVX512):
+            return False
+        try:
+            with open("/proc/cpuinfo") as f:
+                return any("avx512f" in line for line in f if line.startswith("flags"))
+        except OSError:
+            return False
+
+    def __init__(self, use_mkl_sgemm: bool = True, avx512: bool = False):
+        L = self.lib = C.CDLL(self.PATH_AVX512 if avx512 else self.PATH)
+        L.tf_ref_has_avx512.restype = C.c_int
+        self.has_avx512 = bool(L.tf_ref_has_avx512())
+        L.tf_ref_normalize_adjacency.argtypes = [C.c_int, _i32p, _i32p, _f64p]
+        L.tf_ref_normalize_adjacency.restype = C.c_int
         _decl_sched(L, "tf_ref_")
         L.tf_ref_inspect.argtypes = [C.c_int, C.c_int, C.c_int, _i32p, _i32p] + [C.c_int] * 6
         L.tf_ref_inspect.restype = C.c_void_p
@@ -222,6 +238,15 @@ class Ref:
         h = self.lib.tf_ref_inspect(kind, len(ap) - 1, len(ai), ap, ai, threads, iter_per_part, tile_m, bcol,
                                     ccol, data_size)
         return _pull(self.lib, "tf_ref_", h)
+
+    def normalize_adjacency(self, ap, ai, ax):
+        """GnnTensorSpInputs::normalizeAdjacencyMatrix on a copy of the values (doubles, as the reference's
+        CSR holds them); returns the normalised doubles."""
+        x = np.ascontiguousarray(ax, dtype=np.float64).copy()
+        if not self.lib.tf_ref_normalize_adjacency(len(ap) - 1, np.ascontiguousarray(ap, dtype=np.int32),
+                                                   np.ascontiguousarray(ai, dtype=np.int32), x):
+            raise RuntimeError("the reference's normalizeAdjacencyMatrix was not built into oracle/_ref")
+        return x
 
     def spmm(self, ap, ai, ax, b, threads=1):
         out = np.zeros((len(ap) - 1, b.shape[1]), np.float32)

@@ -17,6 +17,13 @@
 //   E3  forwardForOneLayerFusedParallelSeparatedVectorizedSP   fusion/gcn/GCN_Layer_MKL_Forward_Utils.h:218
 //       forwardForOneLayerFusedParallelSeparatedSP (scalar, transposed weight)            :182
 //       forwardForOneLayerWithMKLGeMMAndSpMMSPVectorized (unfused)                        :1138
+//   E2' swiftware::sparse::spmmCsrSpmmCsrFusedVectorized2_32Avx512SP (built only with AVX-512F)
+//         fusion/src/SpMM_SpMM_vectorized.cpp:221
+//   E6  GnnTensorSpInputs::normalizeAdjacencyMatrix
+//         fusion/gcn/SingleLayer/GCN_Single_Layer_SP_Demo_Utils.h:40-53 -- the header itself needs the
+//         un-vendored benchmark framework, so the Makefile cuts exactly this member function out of it
+//         (into _ref/normalize_adjacency.inc) and it is compiled here inside a struct that has the three
+//         fields it touches
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -175,7 +182,15 @@ extern "C" void tf_ref_spmm_csr(int m, int n, const int *Ap, const int *Ai, cons
   else swiftware::sparse::spmmCsrParallel<float>(m, n, m, Ap, Ai, Ax, Bx, Cx, threads);
 }
 
-// variant 0 = scalar E1, 1 = AVX2 E2 (needs n % 32 == 0)
+extern "C" int tf_ref_has_avx512() {
+#ifdef __AVX512F__
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// variant 0 = scalar E1, 1 = AVX2 E2 (needs n % 32 == 0), 2 = AVX-512 (needs n % 32 == 0 and a build with AVX-512F)
 extern "C" void tf_ref_spmm_spmm_fused(int variant, int m, int n, const int *Ap, const int *Ai,
                                        const float *Ax, const int *Bp, const int *Bi, const float *Bx,
                                        const float *Cx, float *Dx, float *ACx, int level_no,
@@ -185,6 +200,12 @@ extern "C" void tf_ref_spmm_spmm_fused(int variant, int m, int n, const int *Ap,
     swiftware::sparse::spmmCsrSpmmCsrFused<float>(m, n, m, m, Ap, Ai, Ax, Bp, Bi, Bx, Cx, Dx, ACx,
                                                   level_no, level_ptr, par_ptr, partition, par_type,
                                                   threads);
+#ifdef __AVX512F__
+  else if (variant == 2)
+    swiftware::sparse::spmmCsrSpmmCsrFusedVectorized2_32Avx512SP(m, n, m, m, Ap, Ai, Ax, Bp, Bi, Bx, Cx,
+                                                                 Dx, ACx, level_no, level_ptr, par_ptr,
+                                                                 partition, par_type, threads);
+#endif
   else
     swiftware::sparse::spmmCsrSpmmCsrFusedVectorized2_32SP(m, n, m, m, Ap, Ai, Ax, Bp, Bi, Bx, Cx, Dx,
                                                            ACx, level_no, level_ptr, par_ptr, partition,
@@ -211,3 +232,30 @@ extern "C" void tf_ref_gemm_spmm_unfused(int m, int *Ap, int *Ai, float *Ax, int
   forwardForOneLayerWithMKLGeMMAndSpMMSPVectorized(m, Ap, Ai, Ax, feat, k, weight, n, out, inter,
                                                    threads);
 }
+
+// ---------------------------------------------------------------------------
+// Adjacency normalisation of the GCN demos: values / sqrt(deg_i * deg_j), deg = row length.
+// ---------------------------------------------------------------------------
+#if __has_include("_ref/normalize_adjacency.inc")
+namespace {
+struct RefNormalize {
+  int *Degrees;
+  size_t NumOfNodes;
+  sym_lib::CSR *AdjacencyMatrix;
+#include "_ref/normalize_adjacency.inc"
+};
+}  // namespace
+// ax: the values as doubles (the reference's CSR holds doubles; its demos convert to float afterwards)
+extern "C" int tf_ref_normalize_adjacency(int n, int *ap, int *ai, double *ax) {
+  sym_lib::CSR a((size_t)n, (size_t)n, (size_t)ap[n], ap, ai, ax);
+  RefNormalize r;
+  r.Degrees = nullptr;
+  r.NumOfNodes = (size_t)n;
+  r.AdjacencyMatrix = &a;
+  r.normalizeAdjacencyMatrix();
+  delete[] r.Degrees;
+  return 1;
+}
+#else
+extern "C" int tf_ref_normalize_adjacency(int, int *, int *, double *) { return 0; }
+#endif

@@ -55,3 +55,11 @@ def same_schedule(a, b):
     if (a.ker_begin is None) != (b.ker_begin is None):
         return False
     return a.ker_begin is None or np.array_equal(a.ker_begin, b.ker_begin)
+
+
+def assert_sums(d, g, what=""):
+    """Whole-output sums of a fixture that keeps only some rows: sum and sum of squares of D."""
+    d64 = np.asarray(d, dtype=np.float64)
+    scale = np.sqrt(float(g["sq"]) * d64.size)
+    assert abs(d64.sum() - float(g["total"])) <= 1e-5 * scale, what + ": sum of D"
+    assert abs((d64 ** 2).sum() - float(g["sq"])) <= 1e-5 * float(g["sq"]), what + ": sum of squares of D"

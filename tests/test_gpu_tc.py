@@ -32,3 +32,24 @@ def test_tc_gemm_rejects_unsupported_shapes(built_lib):
     for k, n in ((30, 64), (64, 47), (64, 512)):
         rc = L.tf_gemm_tc_dev(x.data_ptr(), x.data_ptr(), 0, 8, k, n, x.data_ptr(), None)
         assert rc == _lib.TF_ERR_UNSUPPORTED
+
+
+def test_tensor_core_plan_refuses_unaligned_output(built_lib):
+    """A GeMM-SpMM plan with the tensor-core producer on a graph (no gather tiles) stores D with 16-byte
+    vectors: an output that starts off a 16-byte boundary is refused before anything is launched."""
+    import torch
+    from tile_fusion_b200 import api
+    a = synth.rmat_gcn(7, 3000, 14)
+    A = api.CSRMatrix(3000, 3000, *a)
+    plan = api.Plan("gemm_spmm", A, k=64, n_cols=64)
+    b = torch.zeros((3000, 64), device="cuda")
+    w = torch.zeros((64, 64), device="cuda")
+    d = torch.full((3000 * 64 + 1,), 7.0, device="cuda")
+    with pytest.raises(_lib.TileFusionError) as e:
+        plan.gemm_spmm(b, w, d[1:].view(3000, 64))
+    assert e.value.code == _lib.TF_ERR_ARG
+    torch.cuda.synchronize()
+    assert bool((d == 7.0).all())          # nothing ran
+    plan.gemm_spmm(b, w, d[:3000 * 64].view(3000, 64))
+    plan.status()
+    plan.close()

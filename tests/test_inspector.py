@@ -10,7 +10,7 @@ from tests import common
 from tile_fusion_b200 import _lib, api, synth
 
 MAN = common.manifest()
-SCHED = [k for k, v in MAN.items() if "chain" not in v]
+SCHED = [k for k, v in MAN.items() if "kind" in v and "chain" not in v]
 
 
 def _product_schedule(a, kind, prm):

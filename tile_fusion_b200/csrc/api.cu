@@ -230,9 +230,6 @@ int finish_plan(tf_plan &p, const tf_plan_opts &o, int sm_count, bool ring) {
   if (p.dyn_smem > 0) { p.vec = 4; p.ch = 1; }
   int occ = tfk::stream_occupancy(p.chain, p.vec, p.ch, ring, p.dyn_smem);
   if (occ <= 0) return fail(TF_ERR_CUDA, "occupancy query failed for the executor kernel");
-  if (getenv("TF_DEBUG"))
-    fprintf(stderr, "[tf] chain %d vec %d ch %d ring %d dyn_smem %zu -> %d CTAs/SM\n", p.chain, p.vec, p.ch, (int)ring,
-            p.dyn_smem, occ);
   // The resident-CTA query answers 1 for any kernel that allocates tensor memory.  Two CTAs of this
   // kernel fit an SM (256 of 512 tensor-memory columns each, half the shared memory, 64 registers), and
   // the executor does not depend on the answer for progress: only running CTAs hold tickets.
@@ -580,7 +577,6 @@ tfk::Params base_params(tf_plan &p) {
   P.pt = p.ptile.view();
   P.ct = p.ctile.view();
   P.tile_slots = p.tile_slots;
-  if (const char *f = getenv("TF_DEBUG_FLAGS")) P.debug_flags = atoi(f);
   P.spin_limit = p.spin_limit;
   return P;
 }
@@ -595,9 +591,12 @@ void call_shape(const tf_plan &p, std::initializer_list<const void *> ptrs, int 
   tfk::choose_shape(p.n_cols, a16, vec, ch);
 }
 
+// Plans that run the staged kernel variant -- gather tiles or the tensor-core producer -- use 16-byte vector
+// accesses on the dense operands whatever their width: refuse operands that are not aligned before any launch.
 int check_tiled_alignment(const tf_plan &p, const tfk::Params &P) {
-  if ((p.ptile.on || p.ctile.on) && !(aligned(P.in0, 16) && (!P.out || aligned(P.out, 16))))
-    return fail(TF_ERR_ARG, "gather tiles need 16-byte aligned dense operands (build the plan with tile_slots < 0 otherwise)");
+  if (p.dyn_smem > 0 && !(aligned(P.in0, 16) && (!P.out || aligned(P.out, 16))))
+    return fail(TF_ERR_ARG, "this plan (gather tiles or tensor-core producer) needs 16-byte aligned dense operands "
+                            "(build the plan with tile_slots < 0 and tensor_cores < 0 otherwise)");
   return TF_OK;
 }
 

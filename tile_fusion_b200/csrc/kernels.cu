@@ -349,14 +349,14 @@ __global__ void __launch_bounds__(TILED ? tiled_threads(MODE) : kThreads, TILED 
         return P.inter + (size_t)t * P.n_cols;
       };
       tile_gather<NT, false>(P.pt, rb, P.f_ap, P.f_ax, P.in0, P.n_cols, dst_row, false, 0, 0, 0, stage, hrow,
-                             P.tile_slots, P.debug_flags);
+                             P.tile_slots);
       __syncthreads();
       if (threadIdx.x == 0) publish(P.prod_done, block, P.epoch);
     } else if (TILED && kind == 5) {
       // ---- consume: the rows of one gather tile of the second operator ----
       auto out_row = [&](int r) -> float * { return P.out + (size_t)r * P.n_cols; };
       tile_gather<NT, RING>(P.ct, rb, P.s_ap, P.s_ax, P.inter, P.n_cols, out_row, P.relu != 0, base, P.ring_rows,
-                        P.m_local, stage, hrow, P.tile_slots, P.debug_flags);
+                        P.m_local, stage, hrow, P.tile_slots);
       if (RING) {
         __syncthreads();
         if (threadIdx.x == 0) publish(P.cons_done, block, P.epoch);
@@ -537,12 +537,6 @@ int stream_occupancy(int mode, int vec, int ch, bool ring, size_t dyn_smem) {
       cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem) != cudaSuccess)
     return -1;
   cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, dyn_smem > 0 ? tiled_threads(mode) : kThreads, dyn_smem);
-  if (getenv("TF_DEBUG")) {
-    cudaFuncAttributes a;
-    if (cudaFuncGetAttributes(&a, fn) == cudaSuccess)
-      fprintf(stderr, "[tf] kernel regs %d static smem %zu local %zu maxThreads %d maxDyn %d -> %d\n", a.numRegs,
-              a.sharedSizeBytes, a.localSizeBytes, a.maxThreadsPerBlock, a.maxDynamicSharedSizeBytes, nb);
-  }
   return e == cudaSuccess ? nb : -1;
 }
 

@@ -69,8 +69,6 @@ struct Params {
   // tensor-core dense producer (GeMM-SpMM): TMA descriptors of B and of the split, transposed weight
   alignas(64) CUtensorMap tm_a, tm_whi, tm_wlo;
   int use_tc;
-  int debug_flags;   // diagnostics only (results invalid): 1 = skip the tile compute loop, 2 = skip the tile staging
-                     // copies, 4 = skip the tile stores (tile pipeline)
   TileArrays pt, ct; // gather tiles of the first / second operator (null when not tiled)
   int tile_slots;    // staging slots per CTA (dynamic shared memory holds tile_slots * 132 bytes)
   int tile_rows;     // tile pipeline: most rows of a tile, rounded up to 8
@@ -325,8 +323,7 @@ template <int NT, bool SRC_RING, class DstRow>
 __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, const int *__restrict__ ap,
                                             const float *__restrict__ ax, const float *__restrict__ src,
                                             int n_cols, DstRow dst_row, bool relu, int base, int ring_rows,
-                                            int m_local, float4 *stage, int *hrow, int stage_slots,
-                                            int debug_flags = 0) {
+                                            int m_local, float4 *stage, int *hrow, int stage_slots) {
   const int rp = __ldg(ta.row_ptr + tile), nR = __ldg(ta.row_ptr + tile + 1) - rp;
   const int hp = __ldg(ta.halo_ptr + tile), nH = __ldg(ta.halo_ptr + tile + 1) - hp;
   const int g8 = threadIdx.x >> 3, l8 = threadIdx.x & 7;  // staging: 8 lanes per 128-byte slot
@@ -379,7 +376,7 @@ __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, cons
   const bool dbl = 2 * nH <= stage_slots;
   const int half = dbl ? stage_slots / 2 * 128 : 0;  // byte offset of the second buffer
   auto issue = [&](int c0, int buf) {
-    if (c0 + l8 * 4 < n_cols && !(debug_flags & 2)) {
+    if (c0 + l8 * 4 < n_cols) {
       char *dst = reinterpret_cast<char *>(stage) + buf * half + l8 * 16;
       for (int s = g8; s < nH; s += NT / 8)
         cp_async16(dst + s * 128, src + (size_t)hrow[s] * n_cols + c0 + l8 * 4);
@@ -406,7 +403,7 @@ __device__ __forceinline__ void tile_gather(const TileArrays &ta, int tile, cons
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        if (k < kshort && !(debug_flags & 1)) {  // uniform over the warp
+        if (k < kshort) {  // uniform over the warp
           const int off = __shfl_sync(kFull, ms[j][k >> 2], k & 3, 4);
           const float v = __shfl_sync(kFull, mv[j][k >> 2], k & 3, 4);
           const float4 x = *reinterpret_cast<const float4 *>(bA + off);

@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
         if (lane == 0) nxt = atomicAdd(&st->ticket, 1);  // its latency hides behind this item's checks
         ia = __ldg(P.items + 2 * (size_t)(P.item_begin + cur));
         ib = __ldg(P.items + 2 * (size_t)(P.item_begin + cur) + 1);
-        if (ib.x > 0 && !(P.debug_flags & 16)) {  // diagnostics: 16 = ignore dependences (wrong results)
+        if (ib.x > 0) {
           const bool w = ia.x == 5 ? wait_for(&st->prod_wm, P.prod_done, ib.x, P.epoch, st, limit, lane)
                                    : wait_for(&st->cons_wm, P.cons_done, ib.x, P.epoch, st, limit, lane);
           if (!w) ia.x = -1;
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
 #pragma unroll
       for (int u = 0; u < kPipeIdRegs; ++u) {
         const int s = g8 + 16 * (u * 8 + l8);
-        hid[u] = s < nH ? ((P.debug_flags & 32) ? s : __ldg(ta.halo + hp + s)) : 0;  // diagnostics: 32 = no id loads
+        hid[u] = s < nH ? __ldg(ta.halo + hp + s) : 0;
       }
       for (int c = 0; c < nchunks; ++c, ++g) {
         const int buf = g % kPipeStages;
@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
         const int c0 = c * 32 + l8 * 4;
         char *dst = reinterpret_cast<char *>(stage) + (size_t)buf * buf_bytes + l8 * 16;
         const float *s0 = src + c0;
-        const bool live = c0 < P.n_cols && !(P.debug_flags & 2);
+        const bool live = c0 < P.n_cols;
 #pragma unroll
         for (int u = 0; u < kPipeIdRegs; ++u) {
           if (128 * u >= nH) break;  // uniform over the CTA
@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
           float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
           for (int k = 0; k < kTileMetaNnz; ++k) {
-            if (k < kmax && !(P.debug_flags & 1)) {  // uniform over the warp
+            if (k < kmax) {  // uniform over the warp
               const int2 m = meta[k * nRt + i];       // byte offset of the slot, value bits ({0, 0} past the row's end)
               const float v = __int_as_float(m.y);
               const float4 x = *reinterpret_cast<const float4 *>(bA + m.x);
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) tile_pipeline_kernel(const __
               }
             }
           }
-          if (rc.x >= 0 && !(P.debug_flags & 4)) {
+          if (rc.x >= 0) {
             if (relu) {
               a.x = fmaxf(a.x, 0.f); a.y = fmaxf(a.y, 0.f); a.z = fmaxf(a.z, 0.f); a.w = fmaxf(a.w, 0.f);
               b.x = fmaxf(b.x, 0.f); b.y = fmaxf(b.y, 0.f); b.z = fmaxf(b.z, 0.f); b.w = fmaxf(b.w, 0.f);
