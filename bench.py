@@ -422,16 +422,13 @@ def run_lattice_workload(name, args, ctx, headline):
             step = lambda: plan.gemm_spmm(in0, in1, d)  # noqa: E731
         rc = None
     else:
-        mine = partition.halo_of(a_rows[1], r0, r1)
-        halos = [None] * world
-        dist.all_gather_object(halos, mine)
-        lay = partition.make_layout(rank, bounds, halos)
+        # one C call per step: partition, ncclSend / ncclRecv of the halo rows and the three phases inside the library
+        rc = distributed.NativeRankChain(chain, rank, world, r0, r1, a_rows, n, k=k, dist=dist, device=dev,
+                                         mode=mode)
         if chain == "spmm_spmm":
-            rc = distributed.RankChain("spmm_spmm", lay, a_rows, n, first_rows=(a_rows[0], fi, a_rows[2], len(ids)), device=dev)
-        else:
-            rc = distributed.RankChain("gemm_spmm", lay, a_rows, n, k=k, device=dev)
-        plan = rc.plan
-        step = lambda: rc.step(in0, in1, d, dist=dist)  # noqa: E731
+            assert (rc.info["c_first"], rc.info["c_rows"]) == (lo, hi - lo)
+        plan = api.Plan.adopt(rc)
+        step = lambda: rc.step(in0, in1, d)  # noqa: E731
     setup_s = time.time() - t_setup
 
     def sync_all():
@@ -453,9 +450,11 @@ def run_lattice_workload(name, args, ctx, headline):
             ev[i + 1].record()
         sync_all()
     plan.status()
+    if rc is not None:
+        rc.status()
     total_ms = ev[0].elapsed_time(ev[-1])
     per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
-    launches_per_step = plan.info()["launches"] if world == 1 else (3 if len(rc.lay.boundary_rows) else 2)
+    launches_per_step = plan.info()["launches"] if world == 1 else (3 if rc.info["boundary_rows"] else 2)
     if dist is not None:
         t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -550,7 +549,10 @@ def run_lattice_workload(name, args, ctx, headline):
                "sample": r["sample"], "ms": cpu_ms, "sweep_ms": r["sweep_ms"], "sgemm": r["sgemm"]}
 
     info, tiles = plan.info(), plan.tile_info()
-    plan.close()
+    if rc is not None:
+        rc.close()
+    else:
+        plan.close()
     del d, in0, in1
     torch.cuda.empty_cache()
     if rank != 0:

@@ -226,6 +226,47 @@ int tf_plan_exchange_buffers(tf_plan *p, float **send, long long *send_rows, flo
                              long long *halo_rows);
 
 /* ------------------------------------------------------------------------- */
+/* Several GPUs: one process (or thread) per GPU, rows of A split in consecutive */
+/* blocks, halo rows of the intermediate exchanged over NCCL.  No counterpart in */
+/* the reference, which runs on one shared-memory host.  NCCL (libnccl.so.2) is  */
+/* looked up in the process at run time; TF_ERR_UNSUPPORTED when it is absent.   */
+/* ------------------------------------------------------------------------- */
+typedef struct tf_comm tf_comm;
+typedef struct tf_multi tf_multi;
+/* Rank 0 makes an id (ncclGetUniqueId) and hands it to the other ranks by any means; every rank then joins with
+ * the device that is current in the calling thread.  tf_comm_from_nccl adopts an ncclComm_t the caller already
+ * has (it is not destroyed by tf_comm_free). */
+int tf_comm_unique_id(char id[128]);
+int tf_comm_create(const char id[128], int world, int rank, tf_comm **out);
+int tf_comm_from_nccl(void *nccl_comm, int world, int rank, tf_comm **out);
+void tf_comm_free(tf_comm *c);
+/* Plan for this rank's rows [r0, r1) of the global operator A; `ai` holds GLOBAL column ids; the ranks' ranges must
+ * be consecutive in rank order.  chain 0 = SpMM-SpMM D = A*(A*C), chain 1 = GeMM-SpMM D = A*(B*C) (k = columns of
+ * B).  A collective: every rank of the communicator calls it (the halo lists are all-gathered), then holds
+ *   - the partition arrays: halo = sorted column ids outside [r0, r1), boundary = own rows some other rank's halo
+ *     names, one send and one receive segment per neighbour (tf_partition_layout gives the same arrays on the host);
+ *   - a device plan (tf_plan) with those halo rows and boundary rows. */
+int tf_multi_plan(tf_comm *c, int chain, long long r0, long long r1, const int *ap, const long long *ai, const float *ax,
+                  int k, int n_cols, const tf_plan_opts *opts, tf_multi **out);
+void tf_multi_free(tf_multi *m);
+/* info = {local rows, halo rows, boundary rows, first row of C the rank reads, rows of C it reads (SpMM-SpMM: own
+ * rows plus ghost rows, one contiguous range), send peers, receive peers, threads per CTA of the executor}. */
+int tf_multi_info(const tf_multi *m, long long info[8]);
+tf_plan *tf_multi_plan_handle(tf_multi *m);
+/* One step on this rank, enqueued on `stream` and on the plan's own communication stream: phase 0 (boundary rows of
+ * the intermediate), ncclSend / ncclRecv of those rows, phase 1 beside the exchange, phase 2 after the receive.
+ * in0 = the rank's rows of C (rows [info[3], info[3] + info[4])) or of B; in1 = the weight (GeMM-SpMM) or NULL. */
+int tf_multi_exec(tf_multi *m, const float *in0, const float *in1, int w_transposed, int relu, float *D, void *stream);
+/* Waits for the step's work and reports TF_ERR_TIMEOUT if a bounded wait ran out. */
+int tf_multi_status(tf_multi *m, void *stream);
+/* Host only: the partition arrays of `rank` from every rank's bounds and halo list (halo_ptr[world + 1] into
+ * halo_ids).  malloc'd (tf_free): boundary_rows (local ids); recv and send as {peer, start, count, contiguous}
+ * quadruples, start/count in rows of the halo buffer / of the send buffer. */
+int tf_partition_layout(int rank, int world, const long long *bounds, const long long *halo_ptr,
+                        const long long *halo_ids, long long **boundary_rows, long long *n_boundary,
+                        long long **recv, int *n_recv, long long **send, int *n_send);
+
+/* ------------------------------------------------------------------------- */
 /* Executors, host pointers: the README-level calls                            */
 /*   swiftware::fusion::spMMSpMMExecutor / geMMSpMMExecutor (README.md:31-32)  */
 /* Copies the dense operands to the device, runs, copies D back.              */

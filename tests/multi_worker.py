@@ -54,6 +54,23 @@ def main():
         rg.plan.status()
         want = (A64 @ (b.astype(np.float64) @ w.astype(np.float64)))[r0:r1]
         common.assert_close(d.cpu().numpy(), want, f"rank {rank} GeMM-SpMM {dims}")
+        # the same two chains through the library's own multi-GPU entry points (partition in C++, ncclSend / ncclRecv)
+        nat = distributed.NativeRankChain("spmm_spmm", rank, world, r0, r1, a_rows, n, dist=dist, device=dev)
+        assert (nat.info["c_first"], nat.info["c_rows"]) == (int(ids[0]), len(ids)), nat.info
+        assert nat.info["halo_rows"] == len(lay.halo_ids) and nat.info["boundary_rows"] == len(lay.boundary_rows)
+        d2 = torch.full((r1 - r0, n), float("nan"), device=dev)
+        for _ in range(2):
+            nat.step(c_ext, None, d2)
+        nat.status()
+        want = (A64 @ (A64 @ c.astype(np.float64)))[r0:r1]
+        common.assert_close(d2.cpu().numpy(), want, f"rank {rank} native SpMM-SpMM {dims}")
+        nat.close()
+        nat = distributed.NativeRankChain("gemm_spmm", rank, world, r0, r1, a_rows, n, k=k, dist=dist, device=dev)
+        d2.fill_(float("nan"))
+        nat.step(bd, wd, d2)
+        nat.status()
+        assert torch.equal(d2, d), "native GeMM-SpMM differs from the torch.distributed rank program"
+        nat.close()
         dist.barrier()
     if rank == 0:
         print("multi-GPU parity ok on", world, "ranks")

@@ -5,7 +5,7 @@ import socket
 import numpy as np
 import pytest
 
-from tile_fusion_b200 import partition, synth
+from tile_fusion_b200 import distributed, partition, synth
 
 
 def test_bounds_and_layouts_are_consistent():
@@ -33,6 +33,27 @@ def test_bounds_and_layouts_are_consistent():
             hid = np.concatenate([lay.halo_ids, [-1]])  # world 1: no halo
             back = np.where(loc < lay.m, loc + lay.r0, hid[np.clip(loc - lay.m, 0, len(hid) - 1)])
             np.testing.assert_array_equal(back, rows[g][1])
+
+
+@pytest.mark.parametrize("spec,world,by", [(("lap", (6, 5, 8)), 3, "rows"), (("lap", (40, 33)), 4, "rows"),
+                                           (("rmat_gcn", 5, 1500, 8), 3, "nnz"), (("rmat_gcn", 9, 700, 6), 2, "rows")])
+def test_native_partition_matches(built_lib, spec, world, by):
+    """tf_partition_layout (the C++ partition the multi-GPU entry points use) against partition.make_layout: boundary
+    rows, receive and send segments -- graphs give send segments that are not contiguous in the send buffer."""
+    from tests import common
+    a = common.matrix(spec)
+    n = len(a[0]) - 1
+    bounds = partition.row_bounds(a[0], n, world, by)
+    halos = []
+    for g in range(world):
+        p0, p1 = a[0][bounds[g]], a[0][bounds[g + 1]]
+        halos.append(partition.halo_of(a[1][p0:p1].astype(np.int64), int(bounds[g]), int(bounds[g + 1])))
+    for g in range(world):
+        lay = partition.make_layout(g, bounds, halos)
+        br, rv, sd = distributed.native_layout(g, bounds, halos)
+        assert np.array_equal(br, lay.boundary_rows)
+        assert rv == [(s.peer, s.start, s.count, 1) for s in lay.recv]
+        assert sd == [(s.peer, s.start, s.count, int(s.index is None)) for s in lay.send]
 
 
 def test_nnz_balanced_bounds():
@@ -65,6 +86,11 @@ def _rank_main(rank, world, port, dims, nc, ret):
         halos = [None] * world
         dist.all_gather_object(halos, mine)
         lay = partition.make_layout(rank, bounds, halos)
+        # the library's own (C++) partition gives the same arrays from the gathered halo lists
+        br, rv, sd = distributed.native_layout(rank, bounds, halos)
+        assert np.array_equal(br, lay.boundary_rows)
+        assert rv == [(s.peer, s.start, s.count, 1) for s in lay.recv]
+        assert sd == [(s.peer, s.start, s.count, int(s.index is None)) for s in lay.send]
         # numpy stands in for the device kernels: T rows of this rank = B_local @ W
         b = synth.uniform(2, (n, 8))[r0:r1].astype(np.float64)
         w = synth.uniform(3, (8, nc)).astype(np.float64)

@@ -44,7 +44,9 @@ EXPORTS = [
     "tf_plan_info", "tf_plan_status", "tf_exec_spmm_spmm", "tf_exec_gemm_spmm", "tf_exec_sddmm_spmm",
     "tf_exec_phase", "tf_plan_intermediate", "tf_plan_exchange_buffers", "tf_spmm_spmm_host", "tf_gemm_spmm_host",
     "tf_sddmm_spmm_host", "tf_spmm_dev", "tf_fill_uniform", "tf_fill_normal", "tf_plan_preview", "tf_free", "tf_plan_set_wait_limit", "tf_tiling_preview", "tf_plan_tile_info", "tf_spmm_spmm_noalloc",
-    "tf_noalloc_max_floats", "tf_gemm_tc_dev", "tf_lattice_preview",
+    "tf_noalloc_max_floats", "tf_gemm_tc_dev", "tf_lattice_preview", "tf_comm_unique_id", "tf_comm_create",
+    "tf_comm_from_nccl", "tf_comm_free", "tf_multi_plan", "tf_multi_free", "tf_multi_info", "tf_multi_plan_handle",
+    "tf_multi_exec", "tf_multi_status", "tf_partition_layout",
 ]
 
 _lib = None
@@ -102,6 +104,21 @@ def lib() -> C.CDLL:
     L.tf_noalloc_max_floats.restype = C.c_longlong
     L.tf_gemm_tc_dev.argtypes = [vp, vp, i, i, i, i, vp, vp]
     L.tf_free.restype = None
+    ll = C.c_longlong
+    L.tf_comm_unique_id.argtypes = [vp]
+    L.tf_comm_create.argtypes = [vp, i, i, C.POINTER(vp)]
+    L.tf_comm_from_nccl.argtypes = [vp, i, i, C.POINTER(vp)]
+    L.tf_comm_free.argtypes = [vp]
+    L.tf_comm_free.restype = None
+    L.tf_multi_plan.argtypes = [vp, i, ll, ll, vp, vp, vp, i, i, C.POINTER(PlanOpts), C.POINTER(vp)]
+    L.tf_multi_free.argtypes = [vp]
+    L.tf_multi_free.restype = None
+    L.tf_multi_info.argtypes = [vp, C.POINTER(ll)]
+    L.tf_multi_plan_handle.argtypes = [vp]
+    L.tf_multi_plan_handle.restype = vp
+    L.tf_multi_exec.argtypes = [vp, vp, vp, i, i, vp, vp]
+    L.tf_multi_status.argtypes = [vp, vp]
+    L.tf_partition_layout.argtypes = [i, i, vp, vp, vp, C.POINTER(vp), C.POINTER(ll), C.POINTER(vp), ip, C.POINTER(vp), ip]
     L.tf_lattice_preview.argtypes = [C.POINTER(Csr), i, i, i, ip, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), ip]
     _lib = L
     return L

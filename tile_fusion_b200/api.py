@@ -211,6 +211,16 @@ class Plan:
         self._h = h
         self._schedule = schedule  # keep alive
 
+    @classmethod
+    def adopt(cls, native_chain):
+        """A view of the device plan inside a multi-GPU chain (distributed.NativeRankChain), for info() and status();
+        the chain keeps ownership."""
+        p = cls.__new__(cls)
+        p._h = C.c_void_p(_lib.lib().tf_multi_plan_handle(native_chain._h))
+        p._borrowed = True
+        p._schedule = None
+        return p
+
     # -- information ---------------------------------------------------------
     def info(self) -> dict:
         a = (C.c_longlong * 8)()
@@ -270,7 +280,8 @@ class Plan:
 
     def close(self):
         if getattr(self, "_h", None):
-            _lib.lib().tf_plan_free(self._h)
+            if not getattr(self, "_borrowed", False):
+                _lib.lib().tf_plan_free(self._h)
             self._h = None
 
     def __del__(self):

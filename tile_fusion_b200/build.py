@@ -7,7 +7,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 LIB = os.path.join(HERE, "libtilefusion_b200.so")
-SOURCES = ["kernels.cu", "api.cu", "inspector.cpp", "planner.cpp", "tiling.cpp", "noalloc.cu", "gemm_tc.cu", "tile_pipeline.cu", "lattice.cpp", "lattice_march.cu"]
+SOURCES = ["kernels.cu", "api.cu", "inspector.cpp", "planner.cpp", "tiling.cpp", "noalloc.cu", "gemm_tc.cu", "tile_pipeline.cu", "lattice.cpp", "lattice_march.cu", "multi.cu"]
 HEADERS = ["kernels.cuh", "launch.h", "tf_internal.h", "gemm_tc.cuh", "gemm_tc_host.h", "lattice_march.h"]
 
 
@@ -29,7 +29,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
            "-I" + os.path.join(HERE, "csrc")]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(HERE, "csrc", f) for f in SOURCES] + ["-o", LIB]
+    cmd += [os.path.join(HERE, "csrc", f) for f in SOURCES] + ["-ldl", "-o", LIB]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)

@@ -136,4 +136,19 @@ int build_single_pass_plan(const PlanParams &pp, const int *ap, HostPlan &out);
 
 int check_csr(int m, int ncols, const int *ap, const int *ai, bool need_sorted);
 
+// Row-block partition of a chain over ranks (multi.cu): what one rank exchanges with the others.
+struct ExchangeSegment {
+  int peer;
+  long long start, count;        // rows inside the halo buffer (receive) or the send buffer (send)
+  std::vector<long long> index;  // send side: rows of the send buffer to gather when they are not consecutive
+};
+struct RankLayout {
+  std::vector<long long> halo_ids;       // sorted global ids of the rows of T received
+  std::vector<long long> boundary_rows;  // sorted LOCAL ids of the rows of T sent
+  std::vector<ExchangeSegment> recv, send;
+};
+std::vector<long long> halo_of(const long long *ai, long long nnz, long long r0, long long r1);
+int make_layout(int rank, int world, const long long *bounds, const std::vector<std::vector<long long>> &halos,
+                RankLayout &out);
+
 }  // namespace tf

@@ -100,3 +100,93 @@ class RankChain:
             if exchange is not None:
                 exchange(self)
         self.plan.phase(2, in0, in1, out, w_transposed, relu)
+
+
+class NativeRankChain:
+    """The same rank program behind one C call per step (tf_multi_*): the partition arrays are derived in the
+    library (the halo lists are all-gathered over NCCL), the exchange is ncclSend / ncclRecv on the plan's own
+    stream.  `dist` (torch.distributed, any backend) only carries the 128-byte NCCL id from rank 0 to the others."""
+
+    def __init__(self, chain, rank, world, r0, r1, a_rows, n_cols, *, k=0, dist=None, device=None, **plan_kw):
+        import ctypes as C
+
+        import torch
+
+        from . import _lib
+        L = _lib.lib()
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (C.c_char * 128)()
+            _lib.check(L.tf_comm_unique_id(buf))
+            ident = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).clone()
+        if world > 1:
+            t = ident.to(self.device) if dist.get_backend() == "nccl" else ident
+            dist.broadcast(t, 0)
+            ident = t.cpu()
+        raw = bytes(ident.numpy().tobytes())
+        self._comm = C.c_void_p()
+        _lib.check(L.tf_comm_create(raw, world, rank, C.byref(self._comm)))
+        ap, ai, ax = a_rows
+        ap = np.ascontiguousarray(ap, dtype=np.int32)
+        ai = np.ascontiguousarray(ai, dtype=np.int64)
+        ax = np.ascontiguousarray(ax, dtype=np.float32)
+        o = _lib.PlanOpts(plan_kw.get("mode", 0), plan_kw.get("rows_per_block", 0), 0, -1, 0, 0, 0, None, 0, 0, 0, 0, 0, 0)
+        self._h = C.c_void_p()
+        _lib.check(L.tf_multi_plan(self._comm, 0 if chain == "spmm_spmm" else 1, int(r0), int(r1), ap.ctypes.data,
+                                   ai.ctypes.data, ax.ctypes.data, int(k), int(n_cols), C.byref(o), C.byref(self._h)))
+        info = (C.c_longlong * 8)()
+        _lib.check(L.tf_multi_info(self._h, info))
+        keys = ["rows", "halo_rows", "boundary_rows", "c_first", "c_rows", "send_peers", "recv_peers", "threads"]
+        self.info = dict(zip(keys, [int(x) for x in info]))
+
+    def step(self, in0, in1, out, w_transposed=False, relu=False, stream=None):
+        from . import _lib
+        from .api import _stream_ptr
+        _lib.check(_lib.lib().tf_multi_exec(self._h, in0.data_ptr(), in1.data_ptr() if in1 is not None else None,
+                                            int(w_transposed), int(relu), out.data_ptr(),
+                                            stream if stream is not None else _stream_ptr()))
+
+    def status(self, stream=None):
+        from . import _lib
+        from .api import _stream_ptr
+        _lib.check(_lib.lib().tf_multi_status(self._h, stream if stream is not None else _stream_ptr()))
+
+    def close(self):
+        from . import _lib
+        if getattr(self, "_h", None):
+            _lib.lib().tf_multi_free(self._h)
+            self._h = None
+        if getattr(self, "_comm", None):
+            _lib.lib().tf_comm_free(self._comm)
+            self._comm = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def native_layout(rank, bounds, halos):
+    """The partition arrays of `rank` as the library derives them (tf_partition_layout): (boundary_rows, recv, send)
+    with recv / send as lists of (peer, start, count, contiguous)."""
+    import ctypes as C
+
+    from . import _lib
+    world = len(bounds) - 1
+    b = np.ascontiguousarray(bounds, dtype=np.int64)
+    hp = np.zeros(world + 1, np.int64)
+    np.cumsum([len(h) for h in halos], out=hp[1:])
+    hid = np.ascontiguousarray(np.concatenate([np.asarray(h, dtype=np.int64) for h in halos]) if hp[-1] else np.zeros(1, np.int64))
+    br, rv, sd = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    nb, nr, ns = C.c_longlong(), C.c_int(), C.c_int()
+    _lib.check(_lib.lib().tf_partition_layout(int(rank), world, b.ctypes.data, hp.ctypes.data, hid.ctypes.data, C.byref(br),
+                                              C.byref(nb), C.byref(rv), C.byref(nr), C.byref(sd), C.byref(ns)))
+
+    def take(p, n):
+        a = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_longlong)), shape=(max(n, 1),)).copy()[:n]
+        _lib.lib().tf_free(p)
+        return a
+    return (take(br, nb.value), [tuple(int(v) for v in q) for q in take(rv, 4 * nr.value).reshape(-1, 4)],
+            [tuple(int(v) for v in q) for q in take(sd, 4 * ns.value).reshape(-1, 4)])
