@@ -363,14 +363,24 @@ int tf_multi_exec(tf_multi *m, const float *in0, const float *in1, int w_transpo
   cudaStream_t s = (cudaStream_t)stream;
   const tf::RankLayout &lay = m->lay;
   int rc;
-  if (!lay.boundary_rows.empty()) {
+  // Plans on the plane-marching kernel compute the intermediate inside phase 1, so phase 0 (the boundary rows for
+  // the neighbours, on the general executor with its own state) does not have to precede it: it goes to the
+  // communication stream, in front of the sends, and phase 1 starts at once.
+  long long pinfo[8];
+  tf_plan_info(m->plan, pinfo);
+  const bool phase0_aside = pinfo[5] == 128 && m->chain == 0;
+  const bool exchange = !lay.send.empty() || !lay.recv.empty();
+  if (!lay.boundary_rows.empty() && !(phase0_aside && exchange)) {
     rc = tf_exec_phase(m->plan, 0, in0, in1, w_transposed, relu, nullptr, s);
     if (rc != TF_OK) return rc;
   }
-  const bool exchange = !lay.send.empty() || !lay.recv.empty();
   if (exchange) {
     TF_CUDA(cudaEventRecord(m->ready, s));
     TF_CUDA(cudaStreamWaitEvent(m->comm_stream, m->ready, 0));
+    if (!lay.boundary_rows.empty() && phase0_aside) {
+      rc = tf_exec_phase(m->plan, 0, in0, in1, w_transposed, relu, nullptr, m->comm_stream);
+      if (rc != TF_OK) return rc;
+    }
     for (size_t i = 0; i < lay.send.size(); ++i)
       if (m->gathers[i].idx) {
         gather_rows_kernel<<<(unsigned)std::min<long long>(lay.send[i].count, 1184), 128, 0, m->comm_stream>>>(
