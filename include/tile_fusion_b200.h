@@ -310,6 +310,41 @@ int tf_spmm_spmm_noalloc(const int *Ap, const int *Ai, const float *Ax, int m, c
                          float *D, void *stream);
 long long tf_noalloc_max_floats(void);
 
+/* ------------------------------------------------------------------------- */
+/* Reordered layouts and orderings (host only)                                */
+/* ------------------------------------------------------------------------- */
+/* The rows of the second wave of a two-wave schedule as a CSR of their own, in schedule order: createUnfusedData
+ * (fusion/example/SpMM_SpMM_SP_Demo_Utils.h:600-636).  malloc'd (tf_free): uf_ap[n_rows + 1], uf_ai, uf_ax. */
+int tf_schedule_unfused_csr(const tf_schedule *s, int m, const int *ap, const int *ai, const float *ax, int **uf_ap, int **uf_ai,
+                            float **uf_ax, int *n_rows);
+/* All rows of A in the order the schedule visits them in its second loop, with the old row of every new row (l2_ptr)
+ * and the re-based per-partition pointers (new_mix[2 * (partitions + 1)]): createReorderedAdj
+ * (fusion/gcn/SingleLayer/GCN_Single_Layer_SP_Demo_Utils.h:618-653).  malloc'd (tf_free). */
+int tf_schedule_reordered_adj(const tf_schedule *s, int m, const int *ap, const int *ai, const float *ax, int **r_ap, int **r_ai,
+                              float **r_ax, int **l2_ptr, int **new_mix, int *n_mix);
+/* Reverse Cuthill-McKee ordering of the symmetrised pattern, perm[new] = old (caller-allocated, m entries), and
+ * B = P A P^T with sorted columns (caller-allocated b_ap[m + 1], b_ai / b_ax[ap[m]]).  Stands in for the METIS
+ * reordering front-end of the reference (get_reorderd_matrix, fusion/src/Fusion_Utils.cpp:181-203): a
+ * bandwidth-reducing order brings the columns of a row next to the row, which raises the share of rows both the
+ * reference's criterion and this library's gather tiles can fuse. */
+int tf_rcm_order(int m, const int *ap, const int *ai, int *perm);
+int tf_permute_csr(int m, const int *ap, const int *ai, const float *ax, const int *perm, int *b_ap, int *b_ai, float *b_ax);
+
+/* ------------------------------------------------------------------------- */
+/* Matrix files                                                               */
+/* ------------------------------------------------------------------------- */
+/* Reads a sparse matrix file into CSR (int32 indices, fp32 values, sorted columns; arrays malloc'd, tf_free):
+ *   *.mtx   Matrix Market coordinate format, real / integer / pattern, general / symmetric / skew-symmetric
+ *           (expand_symmetric != 0 mirrors the stored triangle, as the demos' make_full does); duplicates add up;
+ *   *.smtx  the DLMC text format: "rows, cols, nnz", row pointers, column indices; every value 1.
+ * Stands in for get_matrix_from_parameter / readSparseMatrix (fusion/src/Fusion_Utils.cpp:205-272), which exit
+ * the process on a bad file; here a bad file is TF_ERR_ARG / TF_ERR_UNSUPPORTED with a message. */
+int tf_read_matrix(const char *path, int expand_symmetric, int *m, int *n, long long *nnz, int **ap, int **ai,
+                   float **ax);
+/* Dense matrix from a Matrix Market array file (the feature matrices of the GCN demos,
+ * get_dense_matrix_from_parameter, Fusion_Utils.cpp:274-283), returned row-major (malloc'd, tf_free). */
+int tf_read_dense_mtx(const char *path, int *rows, int *cols, float **data);
+
 /* Counter-based seeded fills on the device: uniform[-1,1) is bit-identical to the host
  * generator, N(0, sigma^2) (Box-Muller) agrees with it to float rounding of log/cos;
  * `offset` is the index of the first element. */

@@ -248,6 +248,26 @@ class Ref:
             raise RuntimeError("the reference's normalizeAdjacencyMatrix was not built into oracle/_ref")
         return x
 
+    def layouts(self, kind, ap, ai, ax, threads, iter_per_part=1, tile_m=1, bcol=1, ccol=1):
+        """(createUnfusedData arrays, createReorderedAdj arrays) of the reference for the schedule its own inspector
+        `kind` makes: ((UFAp, UFAi, UFAx), (Ap, Ai, Ax, L2Ptr, NewMixPtr))."""
+        L = self.lib
+        m, nnz = len(ap) - 1, len(ai)
+        h = L.tf_ref_inspect(kind, m, nnz, ap, ai, threads, iter_per_part, tile_m, bcol, ccol, 4)
+        L.tf_ref_create_unfused_data.argtypes = [C.c_void_p, C.c_int, _i32p, _i32p, _f32p, _i32p, _i32p, _f32p]
+        L.tf_ref_create_reordered_adj.argtypes = [C.c_void_p, C.c_int, _i32p, _i32p, _f32p, _i32p, _i32p, _f32p, _i32p, _i32p]
+        ufp, ufi, ufx = np.zeros(m + 1, np.int32), np.zeros(max(nnz, 1), np.int32), np.zeros(max(nnz, 1), np.float32)
+        rows = L.tf_ref_create_unfused_data(C.c_void_p(h), m, ap, ai, ax, ufp, ufi, ufx)
+        if rows < 0:
+            raise RuntimeError("the reference's layout builders were not built into oracle/_ref")
+        rp, ri, rx = np.zeros(m + 1, np.int32), np.zeros(max(nnz, 1), np.int32), np.zeros(max(nnz, 1), np.float32)
+        l2, mix = np.zeros(m, np.int32), np.zeros(4 * m + 8, np.int32)
+        n_mix = L.tf_ref_create_reordered_adj(C.c_void_p(h), m, ap, ai, ax, rp, ri, rx, l2, mix)
+        L.tf_ref_sched_free.argtypes = [C.c_void_p]
+        L.tf_ref_sched_free(C.c_void_p(h))
+        k = int(ufp[rows])
+        return (ufp[:rows + 1], ufi[:k], ufx[:k]), (rp, ri[:nnz], rx[:nnz], l2, mix[:n_mix])
+
     def spmm(self, ap, ai, ax, b, threads=1):
         out = np.zeros((len(ap) - 1, b.shape[1]), np.float32)
         self.lib.tf_ref_spmm_csr(len(ap) - 1, b.shape[1], ap, ai, ax, np.ascontiguousarray(b), out, threads)

@@ -24,6 +24,8 @@
 //         un-vendored benchmark framework, so the Makefile cuts exactly this member function out of it
 //         (into _ref/normalize_adjacency.inc) and it is compiled here inside a struct that has the three
 //         fields it touches
+//   createUnfusedData (fusion/example/SpMM_SpMM_SP_Demo_Utils.h:600-636) and createReorderedAdj
+//         (GCN_Single_Layer_SP_Demo_Utils.h:618-653): the reordered layouts of the bench classes, cut out the same way
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -258,4 +260,59 @@ extern "C" int tf_ref_normalize_adjacency(int n, int *ap, int *ai, double *ax) {
 }
 #else
 extern "C" int tf_ref_normalize_adjacency(int, int *, int *, double *) { return 0; }
+#endif
+
+// ---------------------------------------------------------------------------
+// Reordered layouts of the bench classes (member functions cut out of their headers by the Makefile).
+// ---------------------------------------------------------------------------
+#if __has_include("_ref/create_unfused_data.inc") && __has_include("_ref/create_reordered_adj.inc")
+namespace {
+struct RefUnfusedData {
+  struct In { sym_lib::CSR *ACsr; } in_, *InTensor = &in_;
+  float *AValues = nullptr;
+  int *UFAp = nullptr, *UFAi = nullptr;
+  float *UFAx = nullptr;
+#include "_ref/create_unfused_data.inc"
+};
+struct RefReorderedAdj {
+  struct In { sym_lib::CSR *AdjacencyMatrix; float *AMValues; } in_, *InTensor = &in_;
+  int *Ap = nullptr, *Ai = nullptr, *L2Ptr = nullptr, *NewMixPtr = nullptr;
+  float *Ax = nullptr;
+#include "_ref/create_reordered_adj.inc"
+};
+}  // namespace
+// h: a schedule made by tf_ref_inspect.  Outputs are caller-allocated (uf arrays: at most m + 1 / nnz entries).
+extern "C" int tf_ref_create_unfused_data(void *h, int m, int *ap, int *ai, float *ax, int *uf_ap, int *uf_ai, float *uf_ax) {
+  RefSched *r = (RefSched *)h;
+  sym_lib::CSR a((size_t)m, (size_t)m, (size_t)ap[m], ap, ai, nullptr);
+  RefUnfusedData u;
+  u.in_.ACsr = &a;
+  u.AValues = ax;
+  u.createUnfusedData(r->s->ptr1_, r->s->ker_begin_, r->s->id_);
+  int rows = 0;
+  for (int l1 = r->s->ptr1_[1]; l1 < r->s->ptr1_[2]; ++l1) rows += r->s->ker_begin_[2 * l1 + 1] - r->s->ker_begin_[2 * l1];
+  for (int i = 0; i <= rows; ++i) uf_ap[i] = u.UFAp[i];
+  for (int j = 0; j < u.UFAp[rows]; ++j) { uf_ai[j] = u.UFAi[j]; uf_ax[j] = u.UFAx[j]; }
+  delete[] u.UFAp; delete[] u.UFAi; delete[] u.UFAx;
+  return rows;
+}
+extern "C" int tf_ref_create_reordered_adj(void *h, int m, int *ap, int *ai, float *ax, int *r_ap, int *r_ai, float *r_ax,
+                                           int *l2_ptr, int *new_mix) {
+  RefSched *r = (RefSched *)h;
+  sym_lib::CSR a((size_t)m, (size_t)m, (size_t)ap[m], ap, ai, nullptr);
+  RefReorderedAdj u;
+  u.in_.AdjacencyMatrix = &a;
+  u.in_.AMValues = ax;
+  u.createReorderedAdj(r->s->ptr1_, r->s->ker_begin_, r->s->id_);
+  const int n_mix = (r->s->ptr1_[2] + 1) * 2;
+  for (int i = 0; i <= m; ++i) r_ap[i] = u.Ap[i];
+  for (int j = 0; j < ap[m]; ++j) { r_ai[j] = u.Ai[j]; r_ax[j] = u.Ax[j]; }
+  for (int i = 0; i < m; ++i) l2_ptr[i] = u.L2Ptr[i];
+  for (int i = 0; i < n_mix; ++i) new_mix[i] = u.NewMixPtr[i];
+  delete[] u.Ap; delete[] u.Ai; delete[] u.Ax; delete[] u.L2Ptr; delete[] u.NewMixPtr;
+  return n_mix;
+}
+#else
+extern "C" int tf_ref_create_unfused_data(void *, int, int *, int *, float *, int *, int *, float *) { return -1; }
+extern "C" int tf_ref_create_reordered_adj(void *, int, int *, int *, float *, int *, int *, float *, int *, int *) { return -1; }
 #endif

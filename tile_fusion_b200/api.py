@@ -445,3 +445,73 @@ def lattice_preview(A: CSRMatrix, halo_rows=0, n_cols=128, ctas=148):
     items = take(it, C.c_int, 6 * n.value, np.int32).reshape(-1, 6)
     return dict(nx=nx, ny=ny, nz=nz, ghost_lo=info[4], ghost_hi=info[5], classes=ncls, dict=dic, patch_cls=pcl,
                 items=items)
+
+
+def read_matrix(path: str, expand_symmetric: bool = True) -> CSRMatrix:
+    """A sparse matrix file as a CSRMatrix: Matrix Market coordinate files (*.mtx) and the DLMC text format (*.smtx)
+    -- the two formats the reference's drivers read (fusion/src/Fusion_Utils.cpp:205-272)."""
+    m, n, nnz = C.c_int(), C.c_int(), C.c_longlong()
+    ap, ai, ax = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    check(_lib.lib().tf_read_matrix(str(path).encode(), int(expand_symmetric), C.byref(m), C.byref(n), C.byref(nnz),
+                                    C.byref(ap), C.byref(ai), C.byref(ax)))
+
+    def take(p, ctype, count, dtype):
+        a = np.ctypeslib.as_array(C.cast(p, C.POINTER(ctype)), shape=(max(count, 1),)).copy()[:count].astype(dtype)
+        _lib.lib().tf_free(p)
+        return a
+    return CSRMatrix(m.value, n.value, take(ap, C.c_int, m.value + 1, np.int32), take(ai, C.c_int, nnz.value, np.int32),
+                     take(ax, C.c_float, nnz.value, np.float32))
+
+
+def read_dense_mtx(path: str) -> np.ndarray:
+    """A dense matrix from a Matrix Market array file (fusion/src/Fusion_Utils.cpp:274-283), row-major float32."""
+    r, c, d = C.c_int(), C.c_int(), C.c_void_p()
+    check(_lib.lib().tf_read_dense_mtx(str(path).encode(), C.byref(r), C.byref(c), C.byref(d)))
+    a = np.ctypeslib.as_array(C.cast(d, C.POINTER(C.c_float)), shape=(r.value * c.value,)).copy().reshape(r.value, c.value)
+    _lib.lib().tf_free(d)
+    return a
+
+
+def _take(p, ctype, count, dtype):
+    a = np.ctypeslib.as_array(C.cast(p, C.POINTER(ctype)), shape=(max(count, 1),)).copy()[:count].astype(dtype)
+    _lib.lib().tf_free(p)
+    return a
+
+
+def unfused_csr(schedule: FusedSchedule, A: CSRMatrix):
+    """(UFAp, UFAi, UFAx): the second-wave rows of a schedule as their own CSR, in schedule order
+    (createUnfusedData, fusion/example/SpMM_SpMM_SP_Demo_Utils.h:600-636)."""
+    p, ci, x, n = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_int()
+    check(_lib.lib().tf_schedule_unfused_csr(schedule._h, A.M, A.Ap.ctypes.data, A.Ai.ctypes.data, A.Ax.ctypes.data,
+                                             C.byref(p), C.byref(ci), C.byref(x), C.byref(n)))
+    ap = _take(p, C.c_int, n.value + 1, np.int32)
+    nnz = int(ap[-1])
+    return ap, _take(ci, C.c_int, nnz, np.int32), _take(x, C.c_float, nnz, np.float32)
+
+
+def reordered_adjacency(schedule: FusedSchedule, A: CSRMatrix):
+    """(Ap, Ai, Ax, L2Ptr, NewMixPtr): A's rows in the order the schedule's second loop visits them
+    (createReorderedAdj, fusion/gcn/SingleLayer/GCN_Single_Layer_SP_Demo_Utils.h:618-653)."""
+    ptrs = [C.c_void_p() for _ in range(5)]
+    n = C.c_int()
+    check(_lib.lib().tf_schedule_reordered_adj(schedule._h, A.M, A.Ap.ctypes.data, A.Ai.ctypes.data, A.Ax.ctypes.data,
+                                               *[C.byref(q) for q in ptrs], C.byref(n)))
+    return (_take(ptrs[0], C.c_int, A.M + 1, np.int32), _take(ptrs[1], C.c_int, A.nnz, np.int32),
+            _take(ptrs[2], C.c_float, A.nnz, np.float32), _take(ptrs[3], C.c_int, A.M, np.int32),
+            _take(ptrs[4], C.c_int, n.value, np.int32))
+
+
+def rcm_order(A: CSRMatrix) -> np.ndarray:
+    """Reverse Cuthill-McKee ordering of A's symmetrised pattern: perm[new] = old."""
+    perm = np.empty(A.M, np.int32)
+    check(_lib.lib().tf_rcm_order(A.M, A.Ap.ctypes.data, A.Ai.ctypes.data, perm.ctypes.data))
+    return perm
+
+
+def permute(A: CSRMatrix, perm) -> CSRMatrix:
+    """P A P^T for perm[new] = old, columns sorted."""
+    perm = _i32(perm)
+    ap, ai, ax = np.empty(A.M + 1, np.int32), np.empty(A.nnz, np.int32), np.empty(A.nnz, np.float32)
+    check(_lib.lib().tf_permute_csr(A.M, A.Ap.ctypes.data, A.Ai.ctypes.data, A.Ax.ctypes.data, perm.ctypes.data,
+                                    ap.ctypes.data, ai.ctypes.data, ax.ctypes.data))
+    return CSRMatrix(A.M, A.N, ap, ai, ax)

@@ -319,7 +319,9 @@ int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int halo_rows, int
   M.z_shift = lf.ghost_lo;
   M.planes_c = (long long)lf.nz + lf.ghost_lo + lf.ghost_hi;
   M.halo_lo = halo_rows > 0 && la.ghost_lo; M.halo_hi = halo_rows > 0 && la.ghost_hi;
-  M.grid = sm_count * occ;
+  // With a halo exchange in flight a few SMs are left to the NCCL send / receive kernels: the persistent CTAs of
+  // phase 1 would otherwise hold every SM until they finish, and the exchange would only start then.
+  M.grid = (halo_rows > 0 ? std::max(1, sm_count - 6) : sm_count) * occ;
   // phase 1: the planes of D that need no plane of T from a neighbour rank; phase 2: the first and / or last plane
   const int z1 = M.halo_lo ? 1 : 0, z2 = M.nz - (M.halo_hi ? 1 : 0);
   tf::build_march_items(M.nx, M.ny, z1, z2, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, M.grid, 1, M.host_items);
