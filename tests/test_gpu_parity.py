@@ -138,6 +138,77 @@ def test_plane_march_shapes(torch_cuda, oracle, dims, n_cols):
         ref_plan.close()
 
 
+def _nine_point(nx, ny):
+    import scipy.sparse as sp
+    x, y = np.meshgrid(np.arange(nx), np.arange(ny))
+    r = (y * nx + x).ravel()
+    rows, cols, vals = [], [], []
+    for dy in (-1, 0, 1):
+        for dx in (-1, 0, 1):
+            ok = ((x + dx >= 0) & (x + dx < nx) & (y + dy >= 0) & (y + dy < ny)).ravel()
+            rows.append(r[ok]); cols.append((r + dy * nx + dx)[ok])
+            vals.append(np.full(ok.sum(), 8.0 if dx == 0 and dy == 0 else -1.0, np.float32))
+    S = sp.csr_matrix((np.concatenate(vals), (np.concatenate(rows), np.concatenate(cols))), shape=(nx * ny, nx * ny))
+    S.sort_indices()
+    return S.indptr.astype(np.int32), S.indices.astype(np.int32), S.data.astype(np.float32)
+
+
+def _perturbed_band(n, per_row, half_width, seed):
+    import scipy.sparse as sp
+    rng = np.random.default_rng(seed)
+    rows = np.repeat(np.arange(n), per_row)
+    cols = np.clip(rows + rng.integers(-half_width, half_width + 1, size=rows.size), 0, n - 1)
+    S = sp.csr_matrix((rng.uniform(-1, 1, rows.size).astype(np.float32), (rows, cols)), shape=(n, n))
+    S.sum_duplicates()
+    S.sort_indices()
+    return S.indptr.astype(np.int32), S.indices.astype(np.int32), S.data.astype(np.float32)
+
+
+@pytest.mark.parametrize("which", ["nine_point", "band", "rcm_graph"])
+def test_generic_gather_tiles(torch_cuda, oracle, which):
+    """Patterns that are no 5- / 7-point lattices get gather tiles from runs of consecutive rows (the 9-point
+    operator, a randomly perturbed band, a graph after the RCM ordering): tiles exist, and the tiled executors agree
+    with the oracle's two CSR products and, bit for bit, with the untiled executor."""
+    torch = torch_cuda
+    if which == "nine_point":
+        a = _nine_point(60, 50)
+    elif which == "band":
+        a = _perturbed_band(4000, 12, 40, 1)
+    else:
+        g = synth.rmat_gcn(7, 3000, 14)
+        G = api.CSRMatrix(3000, 3000, *g)
+        P = api.permute(G, api.rcm_order(G))
+        a = (P.Ap, P.Ai, P.Ax)
+    A = _csr(a)
+    for n_cols in (64, 100):
+        c = synth.uniform(3, (A.M, n_cols))
+        want = oracle.spmm(a[0], a[1], a[2], oracle.spmm(a[0], a[1], a[2], c))
+        cd = _dev(torch, c)
+        outs = {}
+        for name, kw in (("pipeline", dict()), ("two_cta", dict(tile_pipeline=-1)), ("untiled", dict(tile_slots=-1))):
+            plan = api.Plan("spmm_spmm", A, n_cols=n_cols, **kw)
+            if name != "untiled" and n_cols % 4 == 0:
+                assert plan.tile_info()["consumer"][3] > 0, (which, name, plan.tile_info())
+            d = torch.full((A.M, n_cols), float("nan"), device="cuda")
+            plan.spmm_spmm(cd, d)
+            plan.status()
+            outs[name] = d
+            common.assert_close(d.cpu().numpy(), want, f"{which} N={n_cols} {name}")
+            plan.close()
+        assert torch.equal(outs["pipeline"], outs["untiled"]) and torch.equal(outs["two_cta"], outs["untiled"])
+    # the dense-producer chain on the same tiles
+    k, n_cols = 32, 64
+    b, w = synth.uniform(2, (A.M, k)), synth.uniform(4, (k, n_cols))
+    plan = api.Plan("gemm_spmm", A, k=k, n_cols=n_cols)
+    assert plan.tile_info()["consumer"][3] > 0
+    d = torch.full((A.M, n_cols), float("nan"), device="cuda")
+    plan.gemm_spmm(_dev(torch, b), _dev(torch, w), d)
+    plan.status()
+    t = (b.astype(np.float64) @ w.astype(np.float64)).astype(np.float32)
+    common.assert_close(d.cpu().numpy(), oracle.spmm(a[0], a[1], a[2], t), f"{which} GeMM-SpMM")
+    plan.close()
+
+
 def test_spmm_spmm_two_operators_and_host_path(torch_cuda, oracle):
     a = common.matrix(MATS["lap2d_40x33"])
     b = common.matrix(("rmat_gcn", 3, 40 * 33, 5))

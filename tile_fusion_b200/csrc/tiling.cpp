@@ -5,8 +5,8 @@
 // tile's own contiguous row range (Fusion_Inspector.h:576,713,886), which leaves nothing fused on a
 // naturally ordered 3-D grid.  Here a tile may be any set of rows.  When the pattern is a lattice --
 // the dominant column offsets are 1, nx and nx*ny, as in grid Laplacians in natural order -- tiles
-// are bx x by x bz bricks, so a staged row is reused by up to seven output rows; otherwise tiling is
-// declined and the executor gathers straight from global memory.
+// are bx x by x bz bricks, so a staged row is reused by up to seven output rows; otherwise tiles are runs of
+// consecutive rows grown against the slot budget, kept when a staged row is reused at least twice.
 #include <algorithm>
 #include <cstdint>
 #include <unordered_map>
@@ -48,11 +48,65 @@ Lattice detect_lattice(int m, const int *ap, const int *ai) {
   return L;
 }
 
+namespace {
+
+// Tiles for any pattern: consecutive rows are added to the open tile until the set of distinct columns they name
+// would pass the slot budget (or the row cap).  The reference's second-wave packer grows its tiles the same way
+// against a cache budget (Fusion_Inspector.h:762-786).  Banded patterns -- FEM matrices, graphs after a
+// bandwidth-reducing ordering -- reuse a staged row several times; where they do not (reuse below 2 nonzeros
+// per staged row) tiling is declined and the executor gathers straight from global memory.
+void build_generic_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_rows, Tiling &out) {
+  out = Tiling();
+  int max_col = m - 1;
+  for (int j = 0; j < ap[m]; ++j) max_col = std::max(max_col, ai[j]);
+  std::vector<int> stamp((size_t)max_col + 1, -1), where((size_t)max_col + 1, 0);
+  out.tile_row_ptr.assign(1, 0);
+  out.tile_halo_ptr.assign(1, 0);
+  out.slot.assign((size_t)ap[m], 0);
+  out.rows.reserve(m);
+  const int row_cap = std::min(max_rows, kTileMaxRows);
+  long long staged = 0;
+  int tile_id = 0, r = 0;
+  while (r < m) {
+    const size_t h0 = out.halo.size();
+    const int r_begin = r;
+    while (r < m && r - r_begin < row_cap) {
+      const size_t before = out.halo.size();
+      for (int j = ap[r]; j < ap[r + 1]; ++j) {
+        const int c = ai[j];
+        if (stamp[c] != tile_id) { stamp[c] = tile_id; out.halo.push_back(c); }
+      }
+      if ((int)(out.halo.size() - h0) > slot_cap) {
+        if (r == r_begin) { out = Tiling(); return; }  // a single row names more columns than a tile can stage
+        for (size_t q = before; q < out.halo.size(); ++q) stamp[out.halo[q]] = -1;
+        out.halo.resize(before);
+        break;
+      }
+      ++r;
+    }
+    std::sort(out.halo.begin() + h0, out.halo.end());
+    for (size_t q = h0; q < out.halo.size(); ++q) where[out.halo[q]] = (int)(q - h0);
+    for (int i = r_begin; i < r; ++i) {
+      out.rows.push_back(i);
+      for (int j = ap[i]; j < ap[i + 1]; ++j) out.slot[j] = (uint16_t)where[ai[j]];
+    }
+    staged += (long long)(out.halo.size() - h0);
+    out.tile_row_ptr.push_back((int)out.rows.size());
+    out.tile_halo_ptr.push_back((int)out.halo.size());
+    ++tile_id;
+  }
+  out.reuse = staged > 0 ? (double)ap[m] / (double)staged : 0.0;
+  out.tiled = out.reuse >= 2.0;
+  if (!out.tiled) out = Tiling();
+}
+
+}  // namespace
+
 int build_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_bz, int max_rows, Tiling &out) {
   out = Tiling();
   if (slot_cap < 64 || slot_cap > 65535) return TF_OK;
   const Lattice L = detect_lattice(m, ap, ai);
-  if (L.dims == 0) return TF_OK;
+  if (L.dims == 0) { build_generic_tiling(m, ap, ai, slot_cap, max_rows, out); return TF_OK; }
   const int nx = L.nx;
   const int ny = L.dims >= 3 ? L.ny : (L.dims == 2 ? (m + nx - 1) / nx : 1);
   const int nz = L.dims >= 3 ? (int)(((long long)m + (long long)nx * ny - 1) / ((long long)nx * ny)) : 1;
@@ -79,7 +133,7 @@ int build_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_bz, 
       }
     }
   }
-  if (bx == 0) return TF_OK;
+  if (bx == 0) { build_generic_tiling(m, ap, ai, slot_cap, max_rows, out); return TF_OK; }
 
   out.nx = nx; out.ny = ny; out.bx = bx; out.by = by; out.bz = bz;
   out.tile_row_ptr.assign(1, 0);
@@ -137,10 +191,10 @@ int build_tiling(int m, const int *ap, const int *ai, int slot_cap, int max_bz, 
           }
         emit(emit, trows.data(), (int)trows.size());
       }
-  if (out.failed || (int)out.rows.size() != m) { out = Tiling(); return TF_OK; }
+  if (out.failed || (int)out.rows.size() != m) { build_generic_tiling(m, ap, ai, slot_cap, max_rows, out); return TF_OK; }
   out.reuse = staged > 0 ? (double)ap[m] / (double)staged : 0.0;
   out.tiled = out.reuse >= 2.0;  // below that, staging costs more than it saves
-  if (!out.tiled) out = Tiling();
+  if (!out.tiled) build_generic_tiling(m, ap, ai, slot_cap, max_rows, out);
   return TF_OK;
 }
 
