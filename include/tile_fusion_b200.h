@@ -192,7 +192,9 @@ int tf_plan_status(tf_plan *p, void *stream);
 
 /* ------------------------------------------------------------------------- */
 /* Executors, device pointers.  `stream` is a cudaStream_t (NULL = default).   */
-/* D is overwritten.                                                          */
+/* D is overwritten.  These calls only enqueue work: a bounded in-kernel wait  */
+/* that ran out is sticky in the plan and is reported (and cleared) by         */
+/* tf_plan_status, which callers of the device path should ask once per batch. */
 /* ------------------------------------------------------------------------- */
 
 /* spmmCsrSpmmCsrFusedVectorized2_32SP (fusion/src/SpMM_SpMM_vectorized.cpp:876) and its scalar
