@@ -195,7 +195,8 @@ def test_generic_gather_tiles(torch_cuda, oracle, which):
             outs[name] = d
             common.assert_close(d.cpu().numpy(), want, f"{which} N={n_cols} {name}")
             plan.close()
-        assert torch.equal(outs["pipeline"], outs["untiled"]) and torch.equal(outs["two_cta"], outs["untiled"])
+        if which != "rcm_graph":  # (a graph's rows of 256 nonzeros or more are reduced by a whole CTA when untiled: another order)
+            assert torch.equal(outs["pipeline"], outs["untiled"]) and torch.equal(outs["two_cta"], outs["untiled"])
     # the dense-producer chain on the same tiles
     k, n_cols = 32, 64
     b, w = synth.uniform(2, (A.M, k)), synth.uniform(4, (k, n_cols))
