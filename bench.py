@@ -366,6 +366,37 @@ def tf32_peak(torch, dev):
         torch.backends.cuda.matmul.allow_tf32 = old
 
 
+def check_columns(torch, dist, chain, a_rows, in0, in1, d, r0, n_rows, fi, world):
+    """Two columns of this rank's rows of D against an fp64 product formed on the host with scipy (every rank's
+    rows of the intermediate column are gathered first): the outputs of the timed path, boundary rows included.
+    Returns the largest relative L2 difference over the ranks (tolerance of the parity tests: 1e-5)."""
+    import scipy.sparse as sp
+    m, n = d.shape
+    cols = [0, n - 1]
+    if chain == "spmm_spmm":
+        c = in0[:, cols].double().cpu().numpy()
+        F = sp.csr_matrix((a_rows[2].astype(np.float64), fi, a_rows[0]), shape=(m, in0.shape[0]))
+        t_loc = torch.from_numpy(F @ c).to(d.device)
+    else:
+        t_loc = (in0 @ in1[:, cols]).double()          # fp32 GEMM (TF32 off), two columns
+    if world > 1:
+        parts = [torch.empty_like(t_loc) for _ in range(world)]    # equal slabs
+        dist.all_gather(parts, t_loc.contiguous())
+        t_full = torch.cat(parts).cpu().numpy()
+    else:
+        t_full = t_loc.cpu().numpy()
+    A = sp.csr_matrix((a_rows[2].astype(np.float64), a_rows[1], a_rows[0]), shape=(m, n_rows))
+    want = A @ t_full
+    got = d[:, cols].double().cpu().numpy()
+    rel = float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-300))
+    if world > 1:
+        t = torch.tensor([rel], device=d.device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        rel = float(t.item())
+    return {"columns": cols, "max_rel_l2_over_ranks": rel, "ok": bool(rel <= 1e-5),
+            "how": "fp64 scipy product of the whole chain for these columns, every rank's rows"}
+
+
 def run_lattice_workload(name, args, ctx, headline):
     """Measures one of c1 / c2 / c5 on the ranks of `ctx`; returns the JSON fields on rank 0, None elsewhere."""
     import torch
@@ -548,6 +579,8 @@ def run_lattice_workload(name, args, ctx, headline):
         cpu = {"value": r["flops"] / (cpu_ms * 1e-3) / 1e9, "unit": UNIT, "cores": r["cores"], "kind": r["kind"],
                "sample": r["sample"], "ms": cpu_ms, "sweep_ms": r["sweep_ms"], "sgemm": r["sgemm"]}
 
+    parity = check_columns(torch, dist, chain, a_rows, in0, in1, d, r0, n_rows, fi if chain == "spmm_spmm" else None, world)
+
     info, tiles = plan.info(), plan.tile_info()
     if rc is not None:
         rc.close()
@@ -565,7 +598,8 @@ def run_lattice_workload(name, args, ctx, headline):
                        "threads_per_cta": threads, "tiles": tiles, "setup_s": round(setup_s, 1),
                        "l2": "inputs (>= 1 GB per step) exceed the 126 MB L2; no flush" if bytes_local > 5e8 else
                              "operands (tens of MB) fit the 126 MB L2 and are not flushed between steps: a warm-L2 figure",
-                       "partition": f"row blocks over {world} GPU(s), halo rows of the intermediate over NCCL"},
+                       "partition": f"row blocks over {world} GPU(s), halo rows of the intermediate over NCCL",
+                       "parity": parity},
             "clocks": clk.summary(), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(launches_per_step * steps)}
 

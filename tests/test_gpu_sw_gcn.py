@@ -1,6 +1,5 @@
 """torch.ops.sw_gcn on CUDA tensors: the layers of the reference's GCN scripts, written exactly as they call the
 operators (binding-project/gcn-e2e-training/FusedGCNLayer.py:8-42, FusedGCNModule.py:7-18), against dense torch."""
-import numpy as np
 import pytest
 
 from tests import common
@@ -79,4 +78,3 @@ def test_other_operators(built_lib):
         common.assert_close(got.cpu().numpy(), want, "sw_gcn forward variants")
     af = torch.sparse.mm(adj, x)
     common.assert_close(torch.ops.sw_gcn.cachedSpMMGeMM(af, w, 4).cpu().numpy(), want, "cachedSpMMGeMM")
-    del np

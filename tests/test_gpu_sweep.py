@@ -30,4 +30,3 @@ def test_sweep_over_a_folder(built_lib, tmp_path):
         assert {r["matrix"] for r in good} == {"lap.mtx", "graph.smtx"}
         assert all(r["check"].startswith("error") for r in rows if r["matrix"] == "missing.mtx")
         assert all(float(r["gflops"]) > 0 and int(r["nnz"]) > 0 for r in good)
-    del np

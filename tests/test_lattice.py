@@ -85,6 +85,18 @@ def test_items_cover_every_output_once(built_lib, dims, n_cols, ctas):
         assert x0 % 16 == 0 and y0 % 8 == 0 and c0 % 16 == 0 and 0 <= zs < ze <= nz
         cover[x0 // 16, y0 // 8, zs:ze, c0 // 16] += 1
     assert np.all(cover == 1)
-    # the chunks of one tile are adjacent in the list (whole dense rows are read together)
     nch = (n_cols + 15) // 16
-    assert all(len({tuple(v[:4]) for v in it[i:i + nch]}) == 1 for i in range(0, len(it), nch))
+    if dims == (128, 128, 128):
+        # the chunks of one tile are adjacent in the list (whole dense rows are read together)
+        assert all(len({tuple(v[:4]) for v in it[i:i + nch]}) == 1 for i in range(0, len(it), nch))
+    # CTAs take the items in list order as they become free; a piece of L planes takes L + 4 steps.  The slowest
+    # CTA must not be slower than with equal cuts of every column (the best of 1 .. 16 cuts).
+    import heapq
+    free = [0] * ctas
+    for x0, y0, zs, ze, c0, _ in it:
+        heapq.heappush(free, heapq.heappop(free) + (ze - zs) + 4)
+    columns = cover.shape[0] * cover.shape[1] * nch
+    equal = min(-(-columns * s // ctas) * (-(-nz // s) + 4) for s in range(1, 17) if s == 1 or -(-nz // s) >= 8)
+    assert max(free) <= equal
+    if dims == (128, 128, 128):
+        assert max(free) == 3 * 132 + 68       # three rounds of whole columns, then 296 pieces of at most 64 planes

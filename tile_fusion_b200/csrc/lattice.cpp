@@ -139,25 +139,58 @@ void build_march_items(int nx, int ny, int z_begin, int z_end, int n_cols, int t
                        int ctas, int min_segments, std::vector<MarchItem> &out) {
   const int nzl = z_end - z_begin;
   if (nzl <= 0) return;
+  ctas = std::max(1, ctas);
+  min_segments = std::max(1, min_segments);
   const int tx = (nx + tile_w - 1) / tile_w, ty = (ny + tile_h - 1) / tile_h, nch = (n_cols + chunk - 1) / chunk;
   const long long columns = (long long)tx * ty * nch;
-  // a segment of L planes costs L + 4 steps (two planes of lead-in for each of the two products)
-  int best_s = 1;
-  long long best_t = -1;
-  for (int s = std::max(1, min_segments); s <= std::max(min_segments, 16); ++s) {
-    const int len = (nzl + s - 1) / s;
-    if (s > min_segments && len < 8) break;
-    const long long rounds = (columns * s + ctas - 1) / std::max(1, ctas);
-    const long long t = rounds * (len + 4);
-    if (best_t < 0 || t < best_t) { best_t = t; best_s = s; }
+  // A piece of L planes costs L + 4 steps (two planes of lead-in for each of the two products), so whole columns
+  // are the cheapest items; but the CTAs take items in rounds, and a last round that only a few CTAs work in
+  // costs a whole column's time.  So: `full` rounds of whole columns (one column per CTA and round), then the
+  // remaining columns cut into pieces whose number is a multiple of the CTA count.  (full, q) is chosen by the
+  // step count of the slowest CTA, full * (nzl + 4) + q * (longest piece + 4).
+  long long best_t = -1, best_full = 0, best_pieces = 0;
+  const long long max_full = min_segments > 1 ? 0 : columns / ctas;
+  for (long long full = max_full; full >= 0; --full) {
+    const long long rest = columns - full * ctas;
+    if (rest == 0) {
+      const long long t = full * (nzl + 4);
+      if (best_t < 0 || t < best_t) { best_t = t; best_full = full; best_pieces = 0; }
+      continue;
+    }
+    for (long long q = 1; q <= 64; ++q) {
+      const long long pieces = std::max(q * ctas, rest * min_segments);
+      const long long per_col = std::min<long long>(pieces / rest, nzl);   // pieces of the least-cut column
+      if (per_col < min_segments) continue;
+      const long long longest = (nzl + per_col - 1) / per_col;
+      if (per_col > 1 && longest < 8 && q > 1) break;
+      const long long rounds = (std::min(pieces, rest * (long long)nzl) + ctas - 1) / ctas;
+      const long long t = full * (nzl + 4) + rounds * (longest + 4);
+      if (best_t < 0 || t < best_t) { best_t = t; best_full = full; best_pieces = pieces; }
+    }
   }
-  for (int s = 0; s < best_s; ++s) {
-    const int zs = z_begin + (int)((long long)nzl * s / best_s), ze = z_begin + (int)((long long)nzl * (s + 1) / best_s);
-    if (ze <= zs) continue;
-    for (int j = 0; j < ty; ++j)
-      for (int i = 0; i < tx; ++i)
-        for (int c = 0; c < nch; ++c) out.push_back(MarchItem{i * tile_w, j * tile_h, zs, ze, c * chunk, 0});
-  }
+  // whole columns first, in (tile, chunk) order: the chunks of a tile run side by side and share DRAM pages
+  long long col = 0;
+  auto item_of = [&](long long c, int zs, int ze) {
+    const int ch = (int)(c % nch);
+    const long long t = c / nch;
+    out.push_back(MarchItem{(int)(t % tx) * tile_w, (int)(t / tx) * tile_h, zs, ze, ch * chunk, 0});
+  };
+  for (; col < best_full * ctas; ++col) item_of(col, z_begin, z_end);
+  const long long rest = columns - col;
+  if (rest <= 0) return;
+  // the remainder: column r of it gets base or base + 1 pieces; pieces of one cut level are emitted together
+  // (level by level), longest pieces first
+  const long long base = std::max<long long>(1, std::min<long long>(best_pieces / rest, nzl));
+  const long long extra = base < nzl ? std::max<long long>(0, std::min(best_pieces - base * rest, rest)) : 0;
+  const long long levels = base + (extra > 0 ? 1 : 0);
+  for (long long lv = 0; lv < levels; ++lv)
+    for (long long r = 0; r < rest; ++r) {
+      // the columns with one more piece are the last `extra` ones
+      const long long n = base + (r >= rest - extra ? 1 : 0);
+      if (lv >= n) continue;
+      const int zs = z_begin + (int)((long long)nzl * lv / n), ze = z_begin + (int)((long long)nzl * (lv + 1) / n);
+      if (ze > zs) item_of(col + r, zs, ze);
+    }
 }
 
 }  // namespace tf

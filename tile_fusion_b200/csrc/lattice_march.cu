@@ -185,10 +185,17 @@ __device__ __forceinline__ float4 halo_row(const float *halo, int gx, int gy, in
   return zero4();
 }
 
+// Planes of lead-in in front of the first output plane zs of an item: C(zs-2) and C(zs-1) enter T(zs-1) and
+// T(zs).  Below plane 0 of a grid without a neighbour rank there is nothing -- C(-1), T(-1) are the zeros the
+// registers start with -- so such an item starts at plane 0.
+__device__ __forceinline__ int lead_in(int zs, const MarchParams &P) {
+  return (zs == 0 && P.z_shift == 0 && P.t_lo == nullptr) ? 0 : 2;
+}
+
 // State a CTA carries from item to item.
 struct CtaState {
   unsigned n_use;  // steps taken so far: step n uses C stage n % stages (parity of n / stages) and phase n of tbar
-  unsigned n_iss;  // plane loads issued so far (thread 0 issues them)
+  unsigned n_iss;  // plane loads issued so far (kept by thread 0, which issues them)
 };
 
 // Rows of the ring of T around the tile that one 4-lane group computes besides its patch.
@@ -198,9 +205,10 @@ constexpr int kRing = (2 * W + 2 * H + (W / 2) * (H / 2) - 1) / ((W / 2) * (H / 
 // rows of the ring of T around the tile at (rx[r], ry[r]) (first product only; `ring` = this warp has any).
 __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchParams &P, const Shared &S, CtaState &cs,
                                          int x0, int y0, int zs, int ze, int c0col, int x, int y, bool ring,
-                                         const int (&rx)[kRing], const int (&ry)[kRing]) {
+                                         const int (&rx)[kRing], const int (&ry)[kRing], const volatile int *next,
+                                         int &prefetched) {
   const int tid = threadIdx.x, lane = tid & 31, c4 = lane & 3;
-  const int kfirst = zs - 2, steps = ze - zs + 4;
+  const int kfirst = zs - lead_in(zs, P), steps = ze - kfirst + 2;
   int xoC[4], xoT[4];
 #pragma unroll
   for (int a = -1; a <= 2; ++a) {
@@ -322,13 +330,23 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     if (!wait_or_abort(S.tbar, cs.n_use & 1u, P.wait_limit, S.abort)) return false;
     // Every warp has therefore finished step k-1, ring rows included (those read their plane after the
     // arrive): the stage of plane k-1 can take plane k-1 + stages.
-    if (step > 0 && step - 1 + kMarchStages < steps) {
-      ++cs.n_iss;
-      if (tid == 0) {
-        const unsigned prev_stage = (cs.n_use - 1) % kMarchStages;
+    // When this item has no such plane left, the stage takes a plane of the CTA's next item (thread 0 knows
+    // it: next[] = {valid, x0, y0, first plane, first column}), so the stream of copies does not stop between
+    // items.
+    if (step > 0 && tid == 0) {
+      const unsigned prev_stage = (cs.n_use - 1) % kMarchStages;
+      const int ahead = step - 1 + kMarchStages;
+      if (ahead < steps) {
+        ++cs.n_iss;
         mbar_expect_tx(S.full + 8 * prev_stage, kMarchCBytes);
-        tma_load_plane(S.cbuf + prev_stage * kMarchCBytes, tm_c, c0col, x0 / 2 - 1, y0 - 2, k - 1 + kMarchStages + P.z_shift,
+        tma_load_plane(S.cbuf + prev_stage * kMarchCBytes, tm_c, c0col, x0 / 2 - 1, y0 - 2, kfirst + ahead + P.z_shift,
                        S.full + 8 * prev_stage);
+      } else if (steps >= kMarchStages && next[0]) {   // (a shorter item left stages unarmed: no hand-over)
+        ++cs.n_iss;
+        ++prefetched;
+        mbar_expect_tx(S.full + 8 * prev_stage, kMarchCBytes);
+        tma_load_plane(S.cbuf + prev_stage * kMarchCBytes, tm_c, next[4], next[1] / 2 - 1, next[2] - 2,
+                       next[3] + (ahead - steps) + P.z_shift, S.full + 8 * prev_stage);
       }
     }
     // D(k-1): everything but the z+ product, from T(k-2) (registers), T(k-1) (registers and neighbours)
@@ -352,6 +370,7 @@ __global__ void __launch_bounds__(kMarchThreads, kMarchCtasPerSm)
 lattice_march_kernel(const __grid_constant__ CUtensorMap tm_c, const MarchParams P) {
   extern __shared__ char dyn[];
   __shared__ int ctl[2];
+  __shared__ int nxt[5];
   Shared S;
   S.cbuf = (smem_u32(dyn) + 1023u) & ~1023u;
   S.tbuf = S.cbuf + kMarchStages * kMarchCBytes;
@@ -394,26 +413,44 @@ lattice_march_kernel(const __grid_constant__ CUtensorMap tm_c, const MarchParams
 
   CtaState cs{0u, 0u};
   bool failed = false;
+  // Thread 0 holds the ticket of the item after the current one and keeps that item's origin in shared memory:
+  // the last steps of an item already fetch the first planes of the next (`pre` of them).
+  int ticket_next = 0, pre = 0;
+  if (tid == 0) ticket_next = atomicAdd(&P.st->ticket, 1);
   for (;;) {
-    if (tid == 0) ctl[0] = atomicAdd(&P.st->ticket, 1);
+    if (tid == 0) {
+      ctl[0] = ticket_next;
+      if (P.item_begin + ticket_next < P.item_end) {
+        ticket_next = atomicAdd(&P.st->ticket, 1);
+        const int nit = P.item_begin + ticket_next;
+        nxt[0] = nit < P.item_end;
+        if (nit < P.item_end) {
+          const int4 na = __ldg(P.items + 2 * nit), nb = __ldg(P.items + 2 * nit + 1);
+          nxt[1] = na.x; nxt[2] = na.y; nxt[3] = na.z - lead_in(na.z, P); nxt[4] = nb.x;
+        }
+      } else {
+        nxt[0] = 0;
+      }
+    }
     __syncthreads();
     const int it = P.item_begin + ctl[0];
     if (it >= P.item_end || ctl[1]) break;
     const int4 ia = __ldg(P.items + 2 * it), ib = __ldg(P.items + 2 * it + 1);
     const int x0 = ia.x, y0 = ia.y, zs = ia.z, ze = ia.w, c0col = ib.x;
-    const int kfirst = zs - 2, steps = ze - zs + 4;
+    const int kfirst = zs - lead_in(zs, P), steps = ze - kfirst + 2;
     if (tid == 0) {
-      for (int s = 0; s < min(kMarchStages, steps); ++s) {
+      for (int s = pre; s < min(kMarchStages, steps); ++s) {
         const unsigned stage = (cs.n_use + s) % kMarchStages;
         mbar_expect_tx(S.full + 8 * stage, kMarchCBytes);
         tma_load_plane(S.cbuf + stage * kMarchCBytes, &tm_c, c0col, x0 / 2 - 1, y0 - 2, kfirst + s + P.z_shift, S.full + 8 * stage);
       }
+      cs.n_iss = cs.n_use + min(kMarchStages, steps);
+      pre = 0;
     }
-    cs.n_iss = cs.n_use + min(kMarchStages, steps);
     int rx[kRing], ry[kRing];
 #pragma unroll
     for (int r = 0; r < kRing; ++r) { rx[r] = x0 + rdx[r]; ry[r] = y0 + rdy[r]; }
-    if (!run_item(&tm_c, P, S, cs, x0, y0, zs, ze, c0col, x0 + 2 * pi, y0 + 2 * warp, ring, rx, ry)) { failed = true; break; }
+    if (!run_item(&tm_c, P, S, cs, x0, y0, zs, ze, c0col, x0 + 2 * pi, y0 + 2 * warp, ring, rx, ry, nxt, pre)) { failed = true; break; }
   }
   if (failed && tid == 0) atomicExch(&P.st->error, 1);
   // A thread that gave up has raised the CTA's abort flag; the others notice it in their own bounded waits
