@@ -142,7 +142,7 @@ struct tf_plan {
     int nx = 0, ny = 0, nz = 0, ncls_f = 0, ncls_a = 0, z_shift = 0, grid = 0, n_items = 0, n_phase1 = 0;
     long long planes_c = 0;
     DevBuf<unsigned> pcls_f, pcls_a;
-    DevBuf<float> dict_f, dict_a;
+    std::vector<float> dict_f, dict_a;   // host copies: the dictionaries travel as kernel parameters
     DevBuf<int4> items;
     DevBuf<tfk::MarchState> st;
     std::vector<tf::MarchItem> host_items;
@@ -338,10 +338,10 @@ int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int halo_rows, int
   M.n_items = (int)M.host_items.size();
   rc = M.items.upload(raw);
   if (rc == TF_OK) rc = M.pcls_f.upload(lf.patch_cls);
-  if (rc == TF_OK) rc = M.dict_f.upload(lf.dict);
+  M.dict_f = lf.dict;
   M.same = &F == &A && halo_rows == 0;
   if (rc == TF_OK && !M.same) rc = M.pcls_a.upload(la.patch_cls);
-  if (rc == TF_OK && !M.same) rc = M.dict_a.upload(la.dict);
+  M.dict_a = M.same ? lf.dict : la.dict;
   if (rc == TF_OK) rc = M.st.alloc(1);
   if (rc != TF_OK) return rc;
   TF_CUDA(cudaMemset(M.st.p, 0, sizeof(tfk::MarchState)));
@@ -361,8 +361,8 @@ int run_march(tf_plan &p, const float *C, float *D, int item_begin, int item_end
   tfk::MarchParams Q;
   std::memset(&Q, 0, sizeof(Q));
   Q.pcls_f = M.pcls_f.p; Q.pcls_a = M.same ? M.pcls_f.p : M.pcls_a.p;
-  Q.dict_f = reinterpret_cast<const float4 *>(M.dict_f.p);
-  Q.dict_a = M.same ? Q.dict_f : reinterpret_cast<const float4 *>(M.dict_a.p);
+  std::memcpy(Q.dict_f, M.dict_f.data(), std::min(sizeof(Q.dict_f), M.dict_f.size() * sizeof(float)));
+  std::memcpy(Q.dict_a, M.dict_a.data(), std::min(sizeof(Q.dict_a), M.dict_a.size() * sizeof(float)));
   Q.ncls_f = M.ncls_f; Q.ncls_a = M.ncls_a;
   Q.out = D;
   Q.items = M.items.p;

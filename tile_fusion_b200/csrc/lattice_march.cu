@@ -79,6 +79,17 @@ __device__ __forceinline__ float4 lds4(unsigned buf, int off) {
   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(buf + off) : "memory");
   return v;
 }
+// The same with a compile-time byte offset in the instruction's address field.
+template <int OFF>
+__device__ __forceinline__ float4 lds4i(unsigned addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr), "n"(OFF) : "memory");
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ void sts4i(unsigned addr, const float4 &v) {
+  asm volatile("st.shared.v4.f32 [%0+%1], {%2, %3, %4, %5};" ::"r"(addr), "n"(OFF), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
 __device__ __forceinline__ void sts4(unsigned buf, int off, const float4 &v) {
   asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(buf + off), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
@@ -90,32 +101,28 @@ __device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.
 // In-plane neighbours of a 2 x 2 patch in a rectangle of pitch P.  xo[a + 1] = byte offset of the patch's
 // column a (-1 .. 2) inside a y-row, lane's 16 bytes included; yo = byte offset of the patch's first y-row.
 // nb: [0, 2) left column, [2, 4) right column, [4, 6) row below, [6, 8) row above.
+// `col[a + 1]` = address of the patch's first y-row at the patch's column a (-1 .. 2), lane's 16 bytes included.
 template <int P>
-__device__ __forceinline__ void load_nb(unsigned buf, const int (&xo)[4], int yo, float4 (&nb)[8]) {
-#pragma unroll
-  for (int b = 0; b < 2; ++b) {
-    nb[b] = lds4(buf, yo + b * (P * 64) + xo[0]);
-    nb[2 + b] = lds4(buf, yo + b * (P * 64) + xo[3]);
-  }
-#pragma unroll
-  for (int a = 0; a < 2; ++a) {
-    nb[4 + a] = lds4(buf, yo - P * 64 + xo[a + 1]);
-    nb[6 + a] = lds4(buf, yo + 2 * (P * 64) + xo[a + 1]);
-  }
+__device__ __forceinline__ void load_nb(const unsigned (&col)[4], float4 (&nb)[8]) {
+  nb[0] = lds4i<0>(col[0]);          nb[1] = lds4i<P * 64>(col[0]);
+  nb[2] = lds4i<0>(col[3]);          nb[3] = lds4i<P * 64>(col[3]);
+  nb[4] = lds4i<-P * 64>(col[1]);    nb[5] = lds4i<-P * 64>(col[2]);
+  nb[6] = lds4i<2 * P * 64>(col[1]); nb[7] = lds4i<2 * P * 64>(col[2]);
 }
 template <int P>
-__device__ __forceinline__ void load_own(unsigned buf, const int (&xo)[4], int yo, float4 (&own)[4]) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) own[j] = lds4(buf, yo + (j >> 1) * (P * 64) + xo[(j & 1) + 1]);
+__device__ __forceinline__ void load_own(const unsigned (&col)[4], float4 (&own)[4]) {
+  own[0] = lds4i<0>(col[1]);      own[1] = lds4i<0>(col[2]);
+  own[2] = lds4i<P * 64>(col[1]); own[3] = lds4i<P * 64>(col[2]);
 }
 
 // Starts one row: acc = its first six products in sorted-column order -- z- (from `zm`, the same grid point one
 // plane down), y-, x-, centre, x+, y+ (this plane); the z+ product is added one step later with the returned
-// coefficient.  The coefficients are entry `cls` of a dictionary in shared memory (two 16-byte loads that
+// coefficient.  The coefficients are entry `cls` of a dictionary in the kernel's parameters (two 16-byte loads that
 // the lanes of a warp mostly share).
-__device__ __forceinline__ float row_start(float4 &acc, unsigned dict, unsigned cls, const float4 &zm, const float4 &ym,
-                                           const float4 &xm, const float4 &c, const float4 &xp, const float4 &yp) {
-  const float4 lo = lds4(dict, 32 * cls), hi = lds4(dict, 32 * cls + 16);
+__device__ __forceinline__ float row_start(float4 &acc, const float4 (&dict)[2 * (kMarchMaxClassesDev + 1)], unsigned cls,
+                                           const float4 &zm, const float4 &ym, const float4 &xm, const float4 &c,
+                                           const float4 &xp, const float4 &yp) {
+  const float4 lo = dict[2 * cls], hi = dict[2 * cls + 1];
   float4 s = fma4(lo.x, zm, zero4());
   s = fma4(lo.y, ym, s);
   s = fma4(lo.z, xm, s);
@@ -125,7 +132,8 @@ __device__ __forceinline__ float row_start(float4 &acc, unsigned dict, unsigned 
   return hi.z;
 }
 // The four rows of a 2 x 2 patch; class of row j = byte j of `word`.
-__device__ __forceinline__ void patch_start(float4 (&acc)[4], float (&czp)[4], unsigned dict, unsigned word,
+__device__ __forceinline__ void patch_start(float4 (&acc)[4], float (&czp)[4],
+                                            const float4 (&dict)[2 * (kMarchMaxClassesDev + 1)], unsigned word,
                                             const float4 (&prev)[4], const float4 (&own)[4], const float4 (&nb)[8]) {
   czp[0] = row_start(acc[0], dict, word & 255u, prev[0], nb[4], nb[0], own[0], own[1], own[2]);
   czp[1] = row_start(acc[1], dict, (word >> 8) & 255u, prev[1], nb[5], own[0], own[1], nb[2], own[3]);
@@ -153,7 +161,6 @@ struct ClassColumn {
 // 32-bit shared-window addresses of the CTA's buffers.
 struct Shared {
   unsigned cbuf, tbuf;       // C stages, the two planes of T
-  unsigned dict_f, dict_a;   // (classes + 1) x 32 bytes each
   unsigned full;             // mbarriers, 8 bytes each: one per C stage (the plane has landed)
   unsigned tbar;             // one phase per step: every warp has stored its rows of T(k-1) (and read C(k))
   volatile int *abort;
@@ -164,6 +171,15 @@ __device__ __forceinline__ void mbar_arrive(unsigned bar) {
 }
 // Bounded wait that also gives up when another thread of the CTA already has.
 __device__ __forceinline__ bool wait_or_abort(unsigned a, unsigned parity, int limit, volatile int *abort) {
+  {
+    unsigned done;   // the usual case: one try, no counters
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(a), "r"(parity) : "memory");
+    if (done) return true;
+  }
   for (int i = 0; i < limit; ++i) {
     unsigned done;
     asm volatile(
@@ -209,13 +225,13 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
                                          int &prefetched) {
   const int tid = threadIdx.x, lane = tid & 31, c4 = lane & 3;
   const int kfirst = zs - lead_in(zs, P), steps = ze - kfirst + 2;
-  int xoC[4], xoT[4];
+  // byte offsets of the patch's first y-row at its columns -1 .. 2, in the C and in the T rectangle
+  int coC[4], coT[4];
 #pragma unroll
   for (int a = -1; a <= 2; ++a) {
-    xoC[a + 1] = xoff<PC>(x - x0 + 2 + a) + c4 * 16;
-    xoT[a + 1] = xoff<PT>(x - x0 + 1 + a) + c4 * 16;
+    coC[a + 1] = (y - y0 + 2) * (PC * 64) + xoff<PC>(x - x0 + 2 + a) + c4 * 16;
+    coT[a + 1] = (y - y0 + 1) * (PT * 64) + xoff<PT>(x - x0 + 1 + a) + c4 * 16;
   }
-  const int yoC = (y - y0 + 2) * (PC * 64), yoT = (y - y0 + 1) * (PT * 64);
   // ring rows: offsets of the row and of its left / right neighbour in the C rectangle, of the row in the T one
   int roC[kRing], roL[kRing], roR[kRing], roT[kRing];
   unsigned rsh[kRing];  // bit position of the row's class in its patch's class word
@@ -243,31 +259,38 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
   ClassColumn cf_col, ca_col;
   cf_col.init(P.pcls_f, x, y, P.nx, P.ny, P.nz, P.pnx, P.pny, 0x01010101u * (unsigned)P.ncls_f);
   ca_col.init(P.pcls_a, x, y, P.nx, P.ny, P.nz, P.pnx, P.pny, 0x01010101u * (unsigned)P.ncls_a);
-  // own rows of C(k-1) and T(k-2), the rows of T and D under way, and the z+ coefficients they still need
-  float4 cprev[4], tprev[4], accT[4], accD[4], rprev[kRing], accR[kRing];
+  // The rows of T and D under way and the z+ coefficients they still need.  The own rows of C(k-1) / C(k), of
+  // T(k-2) / T(k-1), the ring's own rows and the class words live in two sets of registers that swap roles from
+  // step to step (the loop below takes two steps per turn), so nothing is copied between steps.
+  float4 cA[4], cB[4], tA[4], tB[4], accT[4], accD[4], rA[kRing], rB[kRing], accR[kRing];
   float czpT[4], czpD[4], czpR[kRing];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    cprev[j] = zero4(); tprev[j] = zero4(); accT[j] = zero4(); accD[j] = zero4();
+    cA[j] = zero4(); tA[j] = zero4(); accT[j] = zero4(); accD[j] = zero4();
     czpT[j] = 0.f; czpD[j] = 0.f;
   }
-  unsigned wr[kRing];
+  unsigned wrA[kRing], wrB[kRing];
 #pragma unroll
   for (int r = 0; r < kRing; ++r) {
-    rprev[r] = zero4(); accR[r] = zero4(); czpR[r] = 0.f;
-    wr[r] = ring ? cr_col[r].at(kfirst) : 0u;
+    rA[r] = zero4(); accR[r] = zero4(); czpR[r] = 0.f;
+    wrA[r] = ring ? cr_col[r].at(kfirst) : 0u;
   }
-  unsigned wf = cf_col.at(kfirst);
-  unsigned wa = ca_col.zero_word;  // classes of the second operator's rows of plane k - 1
+  unsigned wfA = cf_col.at(kfirst), wfB;
+  unsigned waA = ca_col.zero_word, waB;  // classes of the second operator's rows of plane k - 1
 
-  for (int step = 0; step < steps; ++step) {
+  // One step: plane C(k) arrives.  (cprev, tprev, rprev, wf, wa, wr) were written by the step before;
+  // (own, tcur, rown, wf_next, wa_next, wr_next) are written here.
+  auto one_step = [&](int step, float4 (&cprev)[4], float4 (&own)[4], float4 (&tprev)[4], float4 (&tcur)[4],
+                      float4 (&rprev)[kRing], float4 (&rown)[kRing], unsigned wf, unsigned &wf_next, unsigned wa,
+                      unsigned &wa_next, unsigned (&wr)[kRing], unsigned (&wr_next)[kRing]) -> bool {
     const int k = kfirst + step;
     const unsigned stage = cs.n_use % kMarchStages;
     if (!wait_or_abort(S.full + 8 * stage, (cs.n_use / kMarchStages) & 1u, P.wait_limit, S.abort)) return false;
     const unsigned cb = S.cbuf + stage * kMarchCBytes;
-    float4 own[4], nb[8], tcur[4], rown[kRing];
-    load_own<PC>(cb, xoC, yoC, own);
-    load_nb<PC>(cb, xoC, yoC, nb);
+    float4 nb[8];
+    const unsigned colC[4] = {cb + coC[0], cb + coC[1], cb + coC[2], cb + coC[3]};
+    load_own<PC>(colC, own);
+    load_nb<PC>(colC, nb);
     if (ring) {
 #pragma unroll
       for (int r = 0; r < kRing; ++r) rown[r] = lds4(cb, roC[r]);
@@ -279,10 +302,12 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     for (int j = 0; j < 4; ++j) {
       tcur[j] = fma4(czpT[j], own[j], accT[j]);
       if (halo) tcur[j] = halo_row(halo, x + (j & 1), y + (j >> 1), col, P);
-      // (the buffer of T(k-1) was last read in step k-2; this thread has waited for every warp's arrival of
-      // step k-1, which each warp gives after its reads of step k-2)
-      sts4(tb, yoT + (j >> 1) * (PT * 64) + xoT[(j & 1) + 1], tcur[j]);
     }
+    const unsigned colT[4] = {tb + coT[0], tb + coT[1], tb + coT[2], tb + coT[3]};
+    // (the buffer of T(k-1) was last read in step k-2; this thread has waited for every warp's arrival of
+    // step k-1, which each warp gives after its reads of step k-2)
+    sts4i<0>(colT[1], tcur[0]);       sts4i<0>(colT[2], tcur[1]);
+    sts4i<PT * 64>(colT[1], tcur[2]); sts4i<PT * 64>(colT[2], tcur[3]);
     if (ring) {
 #pragma unroll
       for (int r = 0; r < kRing; ++r) {
@@ -295,8 +320,8 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     if (lane == 0) mbar_arrive(S.tbar);
     // The class words of the next step are fetched only now: the arrive above is a release, which waits
     // for every load the thread has in flight, and a load from global memory can take a microsecond.
-    const unsigned wf_next = cf_col.at(k + 1), wa_next = ca_col.at(k);
-    unsigned wr_next[kRing];
+    wf_next = cf_col.at(k + 1);
+    wa_next = ca_col.at(k);
 #pragma unroll
     for (int r = 0; r < kRing; ++r) wr_next[r] = ring ? cr_col[r].at(k + 1) : 0u;
     // D(k-2) is complete with its z+ product
@@ -309,23 +334,18 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     }
     // T(k): everything but the z+ product
     if (k >= zs - 1 && k <= ze) {
-      patch_start(accT, czpT, S.dict_f, wf, cprev, own, nb);
+      patch_start(accT, czpT, P.dict_f, wf, cprev, own, nb);
       if (ring) {
         // (the ring rows' neighbours are read only now, when the patch's are no longer needed; the stage is
         // refilled one step later, see below)
 #pragma unroll
         for (int r = 0; r < kRing; ++r) {
-          const float4 ym = lds4(cb, roC[r] - PC * 64), xm = lds4(cb, roL[r]), xp = lds4(cb, roR[r]);
-          const float4 yp = lds4(cb, roC[r] + PC * 64);
-          czpR[r] = row_start(accR[r], S.dict_f, (wr[r] >> rsh[r]) & 255u, rprev[r], ym, xm, rown[r], xp, yp);
+          const float4 ym = lds4i<-PC * 64>(cb + roC[r]), xm = lds4(cb, roL[r]), xp = lds4(cb, roR[r]);
+          const float4 yp = lds4i<PC * 64>(cb + roC[r]);
+          czpR[r] = row_start(accR[r], P.dict_f, (wr[r] >> rsh[r]) & 255u, rprev[r], ym, xm, rown[r], xp, yp);
         }
       }
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) cprev[j] = own[j];
-#pragma unroll
-    for (int r = 0; r < kRing; ++r) { rprev[r] = rown[r]; wr[r] = wr_next[r]; }
-    wf = wf_next;
     // every warp has stored its rows of T(k-1) and is done with the plane C(k)
     if (!wait_or_abort(S.tbar, cs.n_use & 1u, P.wait_limit, S.abort)) return false;
     // Every warp has therefore finished step k-1, ring rows included (those read their plane after the
@@ -352,14 +372,18 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     // D(k-1): everything but the z+ product, from T(k-2) (registers), T(k-1) (registers and neighbours)
     if (k - 1 >= zs && k - 1 < ze) {
       float4 tn[8];
-      load_nb<PT>(tb, xoT, yoT, tn);
-      patch_start(accD, czpD, S.dict_a, wa, tprev, tcur, tn);
+      load_nb<PT>(colT, tn);
+      patch_start(accD, czpD, P.dict_a, wa, tprev, tcur, tn);
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) tprev[j] = tcur[j];
-    wa = wa_next;
     ++cs.n_use;
     dptr += plane_floats;
+    return true;
+  };
+
+  for (int step = 0; step < steps; step += 2) {
+    if (!one_step(step, cA, cB, tA, tB, rA, rB, wfA, wfB, waA, waB, wrA, wrB)) return false;
+    if (step + 1 == steps) break;
+    if (!one_step(step + 1, cB, cA, tB, tA, rB, rA, wfB, wfA, waB, waA, wrB, wrA)) return false;
   }
   return true;
 }
@@ -374,15 +398,11 @@ lattice_march_kernel(const __grid_constant__ CUtensorMap tm_c, const MarchParams
   Shared S;
   S.cbuf = (smem_u32(dyn) + 1023u) & ~1023u;
   S.tbuf = S.cbuf + kMarchStages * kMarchCBytes;
-  S.dict_f = S.tbuf + 2 * kMarchTBytes;
-  S.dict_a = S.dict_f + 32 * (kMarchMaxClassesDev + 1);
-  S.full = S.dict_a + 32 * (kMarchMaxClassesDev + 1);
+  S.full = S.tbuf + 2 * kMarchTBytes;
   S.tbar = S.full + 8 * kMarchStages;
   S.abort = &ctl[1];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  for (int i = tid; i < 2 * (P.ncls_f + 1); i += kMarchThreads) sts4(S.dict_f, 16 * i, __ldg(P.dict_f + i));
-  for (int i = tid; i < 2 * (P.ncls_a + 1); i += kMarchThreads) sts4(S.dict_a, 16 * i, __ldg(P.dict_a + i));
   if (tid == 0) {
     for (int s = 0; s < kMarchStages; ++s) mbar_init(S.full + 8 * s, 1);
     mbar_init(S.tbar, kMarchThreads / 32);

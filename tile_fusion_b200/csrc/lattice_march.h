@@ -14,8 +14,7 @@ constexpr int kMarchCtasPerSm = 2;          // two independent CTAs per SM: one 
 constexpr int kMarchCBytes = (kMarchW + 4) * (kMarchH + 4) * kMarchCols * 4;                          // 25 600
 constexpr int kMarchTBytes = ((kMarchW + 2) * (kMarchH + 2) * kMarchCols * 4 + 1023) / 1024 * 1024;  // 21 504
 constexpr int kMarchMaxClassesDev = 63;
-constexpr size_t kMarchSmemBytes = (size_t)kMarchStages * kMarchCBytes + 2 * kMarchTBytes +
-                                   2 * 2 * (kMarchMaxClassesDev + 1) * 16 + kMarchStages * 8 + 1024;
+constexpr size_t kMarchSmemBytes = (size_t)kMarchStages * kMarchCBytes + 2 * kMarchTBytes + (kMarchStages + 1) * 8 + 1024;
 
 struct MarchState {
   int ticket;    // next item
@@ -26,7 +25,6 @@ struct MarchState {
 
 struct MarchParams {
   const unsigned *pcls_f, *pcls_a;  // class words of the first / second operator, [nz][pny][pnx]
-  const float4 *dict_f, *dict_a;    // (classes + 1) x 2 float4: {z-, y-, x-, centre}, {x+, y+, z+, 0}
   int ncls_f, ncls_a;               // the class with this index is the all-zero vector
   float *out;                       // D, nx * ny * nz rows of n_cols
   const float *t_lo, *t_hi;         // planes -1 and nz of T received from the neighbour ranks (null: none)
@@ -36,6 +34,11 @@ struct MarchParams {
   int nx, ny, nz, pnx, pny, n_cols;
   int z_shift;                      // plane of C (in the tensor map) that holds the operand rows of plane 0
   int wait_limit;
+  // Coefficient dictionaries, (classes + 1) x 2 float4 each: {z-, y-, x-, centre}, {x+, y+, z+, 0}.  They travel
+  // as kernel parameters, i.e. in the constant bank: the four lanes that share a row -- usually the whole warp --
+  // read the same entry, which the constant cache serves as one broadcast, while a 16-byte load from shared
+  // memory costs four wavefronts of that pipe whatever the lanes share.
+  float4 dict_f[2 * (kMarchMaxClassesDev + 1)], dict_a[2 * (kMarchMaxClassesDev + 1)];
 };
 
 // Tensor map of C as a 5-D fp32 tensor (n_cols, nx / 2, 2, ny, planes), box = 16 columns x (W+4)/2 x 2 x (H+4) x 1.
