@@ -172,7 +172,8 @@ def test_tiled_plan_emulation(built_lib, dims, slots, max_bz, ring_bytes, slack,
 
 
 def test_tiling_declined_without_structure(built_lib):
-    g = synth.rmat_gcn(3, 3000, 10)
-    assert api.tiling_preview(api.CSRMatrix(3000, 3000, *g)) is None
-    items, info = api.plan_preview(api.CSRMatrix(3000, 3000, *g), n_cols=32)
+    # (a graph this sparse and this large reuses a staged row less than twice, whatever the tile)
+    g = synth.rmat_gcn(3, 20000, 6)
+    assert api.tiling_preview(api.CSRMatrix(20000, 20000, *g)) is None
+    items, info = api.plan_preview(api.CSRMatrix(20000, 20000, *g), n_cols=32)
     assert set(items[:, 0].tolist()) == {0, 1}

@@ -1,13 +1,15 @@
 // Plane-marching executor for SpMM-SpMM chains whose two operators are star stencils on a grid
 // (lattice.cpp): D = A * (F * C), one launch, the intermediate T = F * C never leaves the SM.
 //
-// A work item is an x-y tile of 16 x 16 grid points, a range of planes [zs, ze) and a chunk of 16 dense
-// columns.  The CTA marches along z.  Per step k one plane of C -- the tile grown by two points on every
-// side, 20 x 20 row chunks of 64 bytes -- arrives in shared memory through one 5-D TMA box load
-// (cp.async.bulk.tensor, zero fill outside the grid) that was issued four steps earlier.  The tensor map
-// splits x into (x / 2, x % 2) and lists x / 2 first, so a plane lands as [y][x % 2][x / 2][16 floats]: two
-// patches that are neighbours in x then read addresses exactly 64 bytes apart in every load, i.e. opposite
-// halves of the 32 banks, and the 128-bit loads of a quarter-warp never conflict.  A thread owns a 2 x 2 patch of grid points and four dense columns (one float4 per row):
+// A work item is an x-y tile of 16 x 8 grid points, a range of planes [zs, ze) and a chunk of 16 dense
+// columns.  The CTA (four warps; two CTAs per SM, so one loads while the other computes) marches along z.
+// Per step k one plane of C -- the tile grown by two points on every side, 20 x 12 row chunks of 64 bytes --
+// arrives in shared memory through one 5-D TMA box load (cp.async.bulk.tensor, zero fill outside the grid)
+// that was issued two steps earlier; the copies run on into the CTA's next item.  The tensor map splits x
+// into (x / 2, x % 2) and lists x / 2 first, so a plane lands as [y][x % 2][x / 2][16 floats]: two patches
+// that are neighbours in x then read addresses exactly 64 bytes apart in every load, i.e. opposite halves of
+// the 32 banks, and the 128-bit loads of a quarter-warp never conflict.  A thread owns a 2 x 2 patch of grid
+// points and four dense columns (one float4 per row):
 //   * it reads the patch's own rows and its eight in-plane neighbours of C(k) once (12 loads for 4 rows,
 //     instead of 7 per row),
 //   * adds the z+ product to the rows T(k-1) it has been accumulating, which completes them; they go to a
@@ -17,13 +19,14 @@
 // Products are added in sorted-column order (z-, y-, x-, centre, x+, y+, z+) with fused multiply-adds
 // from a zero accumulator, which is the order of the reference's row loop (SpMM_SpMM.cpp:211-248,
 // SpMM_SpMM_vectorized.cpp:876), so results are bit-identical to the CSR executors; an absent neighbour has
-// coefficient 0.  T is needed one point beyond the tile: four extra warps compute that border ring (2 x 1
-// and 1 x 2 strips).  Coefficients come from the class of each row (one byte per row, a 32-bit word per
-// patch) through a small dictionary in shared memory; a warp whose rows are all of class 0 (interior rows)
-// uses registers instead.
+// coefficient 0.  T is needed one point beyond the tile: three of the four warps also compute two rows each of
+// that border ring per 4-lane group.  Coefficients come from the class of each row (one byte per row, a 32-bit
+// word per patch) through a small dictionary that travels in the kernel's parameters: the constant cache serves
+// the lanes that share an entry in one broadcast, where a 16-byte load from shared memory costs four
+// wavefronts of the pipe that is this kernel's busiest.
 //
-// Every wait is bounded: a thread whose wait runs out raises the abort vote of the step's barrier, the CTA
-// leaves the item loop together, waits (bounded) for its copies in flight, sets the error flag and returns.
+// Every wait is bounded: a thread whose wait runs out raises the CTA's abort flag, the CTA leaves the item
+// loop together, waits (bounded) for its copies in flight, sets the error flag and returns.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -215,14 +218,16 @@ struct CtaState {
 };
 
 // Rows of the ring of T around the tile that one 4-lane group computes besides its patch.
-constexpr int kRing = (2 * W + 2 * H + (W / 2) * (H / 2) - 1) / ((W / 2) * (H / 2));
+constexpr int kRing = 2;
+static_assert(W == 16 && H == 8 && kMarchThreads == 128 && kMarchCols == 16,
+              "the assignment of patches and ring rows to warps is written for 16 x 8 tiles of 16 columns and four warps");
 
 // One work item, seen by one thread: its 2 x 2 patch of the tile at (x, y) (both products) and kRing single
 // rows of the ring of T around the tile at (rx[r], ry[r]) (first product only; `ring` = this warp has any).
 __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchParams &P, const Shared &S, CtaState &cs,
                                          int x0, int y0, int zs, int ze, int c0col, int x, int y, bool ring,
-                                         const int (&rx)[kRing], const int (&ry)[kRing], const volatile int *next,
-                                         int &prefetched) {
+                                         const int (&rx)[kRing], const int (&ry)[kRing], bool pair_x,
+                                         const volatile int *next, int &prefetched) {
   const int tid = threadIdx.x, lane = tid & 31, c4 = lane & 3;
   const int kfirst = zs - lead_in(zs, P), steps = ze - kfirst + 2;
   // byte offsets of the patch's first y-row at its columns -1 .. 2, in the C and in the T rectangle
@@ -338,11 +343,22 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
       if (ring) {
         // (the ring rows' neighbours are read only now, when the patch's are no longer needed; the stage is
         // refilled one step later, see below)
-#pragma unroll
-        for (int r = 0; r < kRing; ++r) {
-          const float4 ym = lds4i<-PC * 64>(cb + roC[r]), xm = lds4(cb, roL[r]), xp = lds4(cb, roR[r]);
-          const float4 yp = lds4i<PC * 64>(cb + roC[r]);
-          czpR[r] = row_start(accR[r], P.dict_f, (wr[r] >> rsh[r]) & 255u, rprev[r], ym, xm, rown[r], xp, yp);
+        if (pair_x) {
+          // the group's two ring rows are neighbours in x: each is the other's x- / x+ row
+          const float4 ym0 = lds4i<-PC * 64>(cb + roC[0]), xm0 = lds4(cb, roL[0]), yp0 = lds4i<PC * 64>(cb + roC[0]);
+          czpR[0] = row_start(accR[0], P.dict_f, (wr[0] >> rsh[0]) & 255u, rprev[0], ym0, xm0, rown[0], rown[kRing - 1], yp0);
+          const float4 ym1 = lds4i<-PC * 64>(cb + roC[kRing - 1]), xp1 = lds4(cb, roR[kRing - 1]);
+          const float4 yp1 = lds4i<PC * 64>(cb + roC[kRing - 1]);
+          czpR[kRing - 1] = row_start(accR[kRing - 1], P.dict_f, (wr[kRing - 1] >> rsh[kRing - 1]) & 255u, rprev[kRing - 1], ym1,
+                                      rown[0], rown[kRing - 1], xp1, yp1);
+        } else {
+          // ... neighbours in y: each is the other's y- / y+ row
+          const float4 ym0 = lds4i<-PC * 64>(cb + roC[0]), xm0 = lds4(cb, roL[0]), xp0 = lds4(cb, roR[0]);
+          czpR[0] = row_start(accR[0], P.dict_f, (wr[0] >> rsh[0]) & 255u, rprev[0], ym0, xm0, rown[0], xp0, rown[kRing - 1]);
+          const float4 xm1 = lds4(cb, roL[kRing - 1]), xp1 = lds4(cb, roR[kRing - 1]);
+          const float4 yp1 = lds4i<PC * 64>(cb + roC[kRing - 1]);
+          czpR[kRing - 1] = row_start(accR[kRing - 1], P.dict_f, (wr[kRing - 1] >> rsh[kRing - 1]) & 255u, rprev[kRing - 1],
+                                      rown[0], xm1, rown[kRing - 1], xp1, yp1);
         }
       }
     }
@@ -419,17 +435,13 @@ lattice_march_kernel(const __grid_constant__ CUtensorMap tm_c, const MarchParams
   // the right row of one y otherwise.
   int rdx[kRing], rdy[kRing];
   bool ring = true;
-  if (H == 16) {  // 64 rows, one per group: warps 0-3 below / above, warps 4-7 left / right
-    if (warp < 4) { rdx[0] = 8 * (warp & 1) + 2 * (pi & 3) + (pi >> 2); rdy[0] = warp < 2 ? -1 : H; }
-    else { rdx[0] = (pi & 1) ? W : -1; rdy[0] = 4 * (warp - 4) + (pi >> 1); }
-  } else {        // 48 rows, two per group of warps 0-2: below, above, left / right
+  // 48 rows, two per group of warps 0-2: below, above, left / right
 #pragma unroll
-    for (int r = 0; r < kRing; ++r) {
-      if (warp < 2) { rdx[r] = 2 * pi + r; rdy[r] = warp == 0 ? -1 : H; }
-      else { rdx[r] = (pi & 1) ? W : -1; rdy[r] = 2 * (pi >> 1) + r; }
-    }
-    ring = warp < 3;
+  for (int r = 0; r < kRing; ++r) {
+    if (warp < 2) { rdx[r] = 2 * pi + r; rdy[r] = warp == 0 ? -1 : H; }
+    else { rdx[r] = (pi & 1) ? W : -1; rdy[r] = 2 * (pi >> 1) + r; }
   }
+  ring = warp < 3;
 
   CtaState cs{0u, 0u};
   bool failed = false;
@@ -470,7 +482,7 @@ lattice_march_kernel(const __grid_constant__ CUtensorMap tm_c, const MarchParams
     int rx[kRing], ry[kRing];
 #pragma unroll
     for (int r = 0; r < kRing; ++r) { rx[r] = x0 + rdx[r]; ry[r] = y0 + rdy[r]; }
-    if (!run_item(&tm_c, P, S, cs, x0, y0, zs, ze, c0col, x0 + 2 * pi, y0 + 2 * warp, ring, rx, ry, nxt, pre)) { failed = true; break; }
+    if (!run_item(&tm_c, P, S, cs, x0, y0, zs, ze, c0col, x0 + 2 * pi, y0 + 2 * warp, ring, rx, ry, warp < 2, nxt, pre)) { failed = true; break; }
   }
   if (failed && tid == 0) atomicExch(&P.st->error, 1);
   // A thread that gave up has raised the CTA's abort flag; the others notice it in their own bounded waits

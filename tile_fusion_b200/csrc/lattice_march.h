@@ -8,11 +8,11 @@ namespace tfk {
 
 constexpr int kMarchW = 16, kMarchH = 8;    // grid points of a tile in x and y
 constexpr int kMarchCols = 16;              // dense columns per chunk (64 bytes per row)
-constexpr int kMarchStages = 4;             // planes of C in flight per CTA
+constexpr int kMarchStages = 3;             // planes of C in flight per CTA (measured: 3 beats 4 and 5; 2 starves)
 constexpr int kMarchThreads = 128;          // 4 warps: 32 patches of 2 x 2 grid points x 4 lanes of 4 columns
 constexpr int kMarchCtasPerSm = 2;          // two independent CTAs per SM: one loads while the other computes
-constexpr int kMarchCBytes = (kMarchW + 4) * (kMarchH + 4) * kMarchCols * 4;                          // 25 600
-constexpr int kMarchTBytes = ((kMarchW + 2) * (kMarchH + 2) * kMarchCols * 4 + 1023) / 1024 * 1024;  // 21 504
+constexpr int kMarchCBytes = (kMarchW + 4) * (kMarchH + 4) * kMarchCols * 4;                          // 15 360
+constexpr int kMarchTBytes = ((kMarchW + 2) * (kMarchH + 2) * kMarchCols * 4 + 1023) / 1024 * 1024;  // 12 288
 constexpr int kMarchMaxClassesDev = 63;
 constexpr size_t kMarchSmemBytes = (size_t)kMarchStages * kMarchCBytes + 2 * kMarchTBytes + (kMarchStages + 1) * 8 + 1024;
 
