@@ -3,6 +3,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <climits>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -144,7 +145,8 @@ struct tf_plan {
     DevBuf<unsigned> pcls_f, pcls_a;
     std::vector<float> dict_f, dict_a;   // host copies: the dictionaries travel as kernel parameters
     DevBuf<int4> items;
-    DevBuf<tfk::MarchState> st;
+    int first_idle_sm = INT_MAX;
+    DevBuf<tfk::MarchState> st;   // [0]: tickets of phase 1 (or of the whole grid), [1]: of phase 2 -- the two may run side by side
     std::vector<tf::MarchItem> host_items;
   } march;
   // schedule mode
@@ -321,10 +323,14 @@ int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int halo_rows, int
   M.halo_lo = halo_rows > 0 && la.ghost_lo; M.halo_hi = halo_rows > 0 && la.ghost_hi;
   // With a halo exchange in flight a few SMs are left to the NCCL send / receive kernels: the persistent CTAs of
   // phase 1 would otherwise hold every SM until they finish, and the exchange would only start then.
-  M.grid = (halo_rows > 0 ? std::max(1, sm_count - 6) : sm_count) * occ;
+  // With neighbour ranks the last SMs stay free while phase 1 runs: the kernels of the halo exchange and phase 2
+  // start there, beside the persistent CTAs.
+  M.grid = sm_count * occ;
+  M.first_idle_sm = halo_rows > 0 ? std::max(1, sm_count - 6) : INT_MAX;
+  const int working = std::min(sm_count, M.first_idle_sm) * occ;
   // phase 1: the planes of D that need no plane of T from a neighbour rank; phase 2: the first and / or last plane
   const int z1 = M.halo_lo ? 1 : 0, z2 = M.nz - (M.halo_hi ? 1 : 0);
-  tf::build_march_items(M.nx, M.ny, z1, z2, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, M.grid, 1, M.host_items);
+  tf::build_march_items(M.nx, M.ny, z1, z2, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, working, 1, M.host_items);
   M.n_phase1 = (int)M.host_items.size();
   if (M.halo_lo) tf::build_march_items(M.nx, M.ny, 0, 1, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, M.grid, 1, M.host_items);
   if (M.halo_hi && M.nz > 1)
@@ -342,9 +348,9 @@ int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int halo_rows, int
   M.same = &F == &A && halo_rows == 0;
   if (rc == TF_OK && !M.same) rc = M.pcls_a.upload(la.patch_cls);
   M.dict_a = M.same ? lf.dict : la.dict;
-  if (rc == TF_OK) rc = M.st.alloc(1);
+  if (rc == TF_OK) rc = M.st.alloc(2);
   if (rc != TF_OK) return rc;
-  TF_CUDA(cudaMemset(M.st.p, 0, sizeof(tfk::MarchState)));
+  TF_CUDA(cudaMemset(M.st.p, 0, 2 * sizeof(tfk::MarchState)));
   M.on = true;
   return TF_OK;
 }
@@ -367,7 +373,7 @@ int run_march(tf_plan &p, const float *C, float *D, int item_begin, int item_end
   Q.out = D;
   Q.items = M.items.p;
   Q.item_begin = item_begin; Q.item_end = item_end;
-  Q.st = M.st.p;
+  Q.st = M.st.p + (with_halo ? 1 : 0);
   Q.nx = M.nx; Q.ny = M.ny; Q.nz = M.nz;
   Q.pnx = (M.nx + 1) / 2; Q.pny = (M.ny + 1) / 2;
   Q.n_cols = p.n_cols;
@@ -379,7 +385,10 @@ int run_march(tf_plan &p, const float *C, float *D, int item_begin, int item_end
     if (M.halo_hi) Q.t_hi = halo + (M.halo_lo ? plane : 0);
   }
   Q.wait_limit = p.spin_limit;
-  TF_CUDA(tfk::launch_lattice_march(std::min(M.grid, std::max(1, item_end - item_begin)), tm, Q, s));
+  // phase 1 of a plan with neighbour ranks keeps the last SMs free; every other launch uses what it finds
+  const bool keep_free = !with_halo && p.halo_rows > 0;
+  Q.first_idle_sm = keep_free ? M.first_idle_sm : INT_MAX;
+  TF_CUDA(tfk::launch_lattice_march(keep_free ? M.grid : std::min(M.grid, std::max(1, item_end - item_begin)), tm, Q, s));
   p.launches = 1;
   return TF_OK;
 }
@@ -870,9 +879,9 @@ int tf_plan_status(tf_plan *p, void *stream) {
   if (rc != TF_OK) return rc;
   TF_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
   if (p->march.on) {
-    tfk::MarchState ms;
-    TF_CUDA(cudaMemcpy(&ms, p->march.st.p, sizeof(ms), cudaMemcpyDeviceToHost));
-    if (ms.error) {
+    tfk::MarchState ms[2];
+    TF_CUDA(cudaMemcpy(ms, p->march.st.p, sizeof(ms), cudaMemcpyDeviceToHost));
+    if (ms[0].error || ms[1].error) {
       cudaMemset(p->march.st.p, 0, sizeof(ms));
       return fail(TF_ERR_TIMEOUT, "a bounded in-kernel wait ran out; the output of the last call is not valid");
     }

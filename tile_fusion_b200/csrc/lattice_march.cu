@@ -443,13 +443,20 @@ lattice_march_kernel(const __grid_constant__ CUtensorMap tm_c, const MarchParams
   }
   ring = warp < 3;
 
+  // SMs kept free for another kernel (the halo exchange of a multi-GPU step): the grid covers every SM, and the
+  // CTAs that find themselves on one of the last SMs take no item.  A smaller grid would not do: the hardware
+  // spreads a grid over all SMs before it doubles up, so no SM would stay empty.
+  unsigned smid;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+  const bool idle = (int)smid >= P.first_idle_sm;
+
   CtaState cs{0u, 0u};
   bool failed = false;
   // Thread 0 holds the ticket of the item after the current one and keeps that item's origin in shared memory:
   // the last steps of an item already fetch the first planes of the next (`pre` of them).
   int ticket_next = 0, pre = 0;
-  if (tid == 0) ticket_next = atomicAdd(&P.st->ticket, 1);
-  for (;;) {
+  if (tid == 0 && !idle) ticket_next = atomicAdd(&P.st->ticket, 1);
+  for (; !idle;) {
     if (tid == 0) {
       ctl[0] = ticket_next;
       if (P.item_begin + ticket_next < P.item_end) {

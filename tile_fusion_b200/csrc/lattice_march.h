@@ -34,6 +34,7 @@ struct MarchParams {
   int nx, ny, nz, pnx, pny, n_cols;
   int z_shift;                      // plane of C (in the tensor map) that holds the operand rows of plane 0
   int wait_limit;
+  int first_idle_sm;                // CTAs that land on an SM with this id or a higher one leave at once (see api.cu)
   // Coefficient dictionaries, (classes + 1) x 2 float4 each: {z-, y-, x-, centre}, {x+, y+, z+, 0}.  They travel
   // as kernel parameters, i.e. in the constant bank: the four lanes that share a row -- usually the whole warp --
   // read the same entry, which the constant cache serves as one broadcast, while a 16-byte load from shared

@@ -15,6 +15,7 @@
 #include <dlfcn.h>
 
 #include <algorithm>
+#include <climits>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -112,9 +113,22 @@ using tf::fail;
 
 typedef struct { char internal[128]; } NcclUniqueId;  // ncclUniqueId
 typedef void *NcclComm;                               // ncclComm_t
+// ncclConfig_t as NCCL 2.17 declared it (newer libraries accept it by its size and version fields and default what
+// it lacks).  The one field set here is maxCTAs: the exchange kernel of a step must fit on the few SMs the
+// marching kernel leaves free -- with NCCL's default of up to 32 CTAs most of them would wait for an SM until phase 1
+// has ended, and the receive with them.
+struct NcclConfig217 {
+  size_t size;
+  unsigned magic, version;
+  int blocking, cga_cluster_size, min_ctas, max_ctas;
+  const char *net_name;
+};
+constexpr int kExchangeCtas = 4;
+
 struct Nccl {
   int (*GetUniqueId)(NcclUniqueId *) = nullptr;
   int (*CommInitRank)(NcclComm *, int, NcclUniqueId, int) = nullptr;
+  int (*CommInitRankConfig)(NcclComm *, int, NcclUniqueId, int, NcclConfig217 *) = nullptr;  // optional (NCCL >= 2.17)
   int (*CommDestroy)(NcclComm) = nullptr;
   int (*Send)(const void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
   int (*Recv)(void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
@@ -136,6 +150,7 @@ Nccl &nccl() {
   if (!h) return n;
   n.GetUniqueId = (int (*)(NcclUniqueId *))dlsym(h, "ncclGetUniqueId");
   n.CommInitRank = (int (*)(NcclComm *, int, NcclUniqueId, int))dlsym(h, "ncclCommInitRank");
+  n.CommInitRankConfig = (int (*)(NcclComm *, int, NcclUniqueId, int, NcclConfig217 *))dlsym(h, "ncclCommInitRankConfig");
   n.CommDestroy = (int (*)(NcclComm))dlsym(h, "ncclCommDestroy");
   n.Send = (int (*)(const void *, size_t, int, int, NcclComm, cudaStream_t))dlsym(h, "ncclSend");
   n.Recv = (int (*)(void *, size_t, int, int, NcclComm, cudaStream_t))dlsym(h, "ncclRecv");
@@ -214,7 +229,16 @@ int tf_comm_create(const char id[128], int world, int rank, tf_comm **out) {
   TF_CUDA(cudaGetDevice(&c->device));
   NcclUniqueId u;
   std::memcpy(u.internal, id, 128);
-  TF_NCCL(nccl().CommInitRank(&c->comm, world, u, rank));
+  if (nccl().CommInitRankConfig) {
+    NcclConfig217 cfg;
+    cfg.size = sizeof(cfg); cfg.magic = 0xcafebeefu; cfg.version = 21700;
+    cfg.blocking = INT_MIN; cfg.cga_cluster_size = INT_MIN;   // INT_MIN: left to the library
+    cfg.min_ctas = 1; cfg.max_ctas = kExchangeCtas;
+    cfg.net_name = nullptr;
+    TF_NCCL(nccl().CommInitRankConfig(&c->comm, world, u, rank, &cfg));
+  } else {
+    TF_NCCL(nccl().CommInitRank(&c->comm, world, u, rank));
+  }
   *out = c.release();
   return TF_OK;
 }
@@ -363,24 +387,18 @@ int tf_multi_exec(tf_multi *m, const float *in0, const float *in1, int w_transpo
   cudaStream_t s = (cudaStream_t)stream;
   const tf::RankLayout &lay = m->lay;
   int rc;
-  // Plans on the plane-marching kernel compute the intermediate inside phase 1, so phase 0 (the boundary rows for
-  // the neighbours, on the general executor with its own state) does not have to precede it: it goes to the
-  // communication stream, in front of the sends, and phase 1 starts at once.
   long long pinfo[8];
   tf_plan_info(m->plan, pinfo);
-  const bool phase0_aside = pinfo[5] == 128 && m->chain == 0;
+  const bool marching = pinfo[5] == 128 && m->chain == 0;
   const bool exchange = !lay.send.empty() || !lay.recv.empty();
-  if (!lay.boundary_rows.empty() && !(phase0_aside && exchange)) {
+  // Phase 0 (the boundary rows for the neighbours) is short and goes first, on every SM.
+  if (!lay.boundary_rows.empty()) {
     rc = tf_exec_phase(m->plan, 0, in0, in1, w_transposed, relu, nullptr, s);
     if (rc != TF_OK) return rc;
   }
   if (exchange) {
     TF_CUDA(cudaEventRecord(m->ready, s));
     TF_CUDA(cudaStreamWaitEvent(m->comm_stream, m->ready, 0));
-    if (!lay.boundary_rows.empty() && phase0_aside) {
-      rc = tf_exec_phase(m->plan, 0, in0, in1, w_transposed, relu, nullptr, m->comm_stream);
-      if (rc != TF_OK) return rc;
-    }
     for (size_t i = 0; i < lay.send.size(); ++i)
       if (m->gathers[i].idx) {
         gather_rows_kernel<<<(unsigned)std::min<long long>(lay.send[i].count, 1184), 128, 0, m->comm_stream>>>(
@@ -397,6 +415,19 @@ int tf_multi_exec(tf_multi *m, const float *in0, const float *in1, int w_transpo
                           m->comm_stream));
     TF_NCCL(nccl().GroupEnd());
     TF_CUDA(cudaEventRecord(m->arrived, m->comm_stream));
+  }
+  if (marching && exchange) {
+    // Plane-marching plans compute the intermediate inside phase 1, which therefore does not wait for anything.
+    // Phase 2 (the first / last plane of D, with its own ticket state) follows the receive on the communication
+    // stream and runs beside phase 1 -- on the SMs phase 1 leaves free for the exchange, then on those its CTAs
+    // give up -- instead of after it.
+    rc = tf_exec_phase(m->plan, 2, in0, in1, w_transposed, relu, D, m->comm_stream);
+    if (rc != TF_OK) return rc;
+    TF_CUDA(cudaEventRecord(m->arrived, m->comm_stream));
+    rc = tf_exec_phase(m->plan, 1, in0, in1, w_transposed, relu, D, s);
+    if (rc != TF_OK) return rc;
+    TF_CUDA(cudaStreamWaitEvent(s, m->arrived, 0));
+    return TF_OK;
   }
   rc = tf_exec_phase(m->plan, 1, in0, in1, w_transposed, relu, D, s);
   if (rc != TF_OK) return rc;
