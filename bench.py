@@ -481,8 +481,20 @@ def run_lattice_workload(name, args, ctx, headline):
             ev[i + 1].record()
         sync_all()
     plan.status()
+    step_trace = None
     if rc is not None:
         rc.status()
+        # one more step, traced: where each rank's step spends its time (ms from the step's start)
+        rc.trace(True)
+        sync_all()
+        step()
+        mine = rc.trace(False) or {}
+        t = torch.tensor([mine.get(k, -1.0) for k in ("phase0_done", "exchange_done", "phase2_done", "phase1_done", "step_done")],
+                         device=dev, dtype=torch.float32)
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t)
+        step_trace = {"columns": ["phase0_done", "exchange_done", "phase2_done", "phase1_done", "step_done"],
+                      "ms_from_step_start_per_rank": [[round(float(v), 4) for v in p.tolist()] for p in parts]}
     total_ms = ev[0].elapsed_time(ev[-1])
     per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
     launches_per_step = plan.info()["launches"] if world == 1 else (3 if rc.info["boundary_rows"] else 2)
@@ -599,7 +611,7 @@ def run_lattice_workload(name, args, ctx, headline):
                        "l2": "inputs (>= 1 GB per step) exceed the 126 MB L2; no flush" if bytes_local > 5e8 else
                              "operands (tens of MB) fit the 126 MB L2 and are not flushed between steps: a warm-L2 figure",
                        "partition": f"row blocks over {world} GPU(s), halo rows of the intermediate over NCCL",
-                       "parity": parity},
+                       "parity": parity, **({"step_trace": step_trace} if step_trace else {})},
             "clocks": clk.summary(), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(launches_per_step * steps)}
 

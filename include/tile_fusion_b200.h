@@ -261,6 +261,11 @@ tf_plan *tf_multi_plan_handle(tf_multi *m);
 int tf_multi_exec(tf_multi *m, const float *in0, const float *in1, int w_transposed, int relu, float *D, void *stream);
 /* Waits for the step's work and reports TF_ERR_TIMEOUT if a bounded wait ran out. */
 int tf_multi_status(tf_multi *m, void *stream);
+/* Step tracing (the reference times its executors with a wall clock around execute(), SWTensorBench.h; a step here
+ * spans two streams).  on != 0: following steps record CUDA events around their phases.  ms (may be NULL) receives
+ * the last traced step's times in milliseconds from its start: {phase 0 done, exchange done, phase 2 done,
+ * phase 1 done, step done}; -1 where nothing was recorded.  Synchronises the device when ms is given. */
+int tf_multi_trace(tf_multi *m, int on, float ms[5]);
 /* Host only: the partition arrays of `rank` from every rank's bounds and halo list (halo_ptr[world + 1] into
  * halo_ids).  malloc'd (tf_free): boundary_rows (local ids); recv and send as {peer, start, count, contiguous}
  * quadruples, start/count in rows of the halo buffer / of the send buffer. */

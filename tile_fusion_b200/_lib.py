@@ -46,7 +46,7 @@ EXPORTS = [
     "tf_sddmm_spmm_host", "tf_spmm_dev", "tf_fill_uniform", "tf_fill_normal", "tf_plan_preview", "tf_free", "tf_plan_set_wait_limit", "tf_tiling_preview", "tf_plan_tile_info", "tf_spmm_spmm_noalloc",
     "tf_noalloc_max_floats", "tf_gemm_tc_dev", "tf_lattice_preview", "tf_comm_unique_id", "tf_comm_create",
     "tf_comm_from_nccl", "tf_comm_free", "tf_multi_plan", "tf_multi_free", "tf_multi_info", "tf_multi_plan_handle",
-    "tf_multi_exec", "tf_multi_status", "tf_partition_layout", "tf_read_matrix", "tf_read_dense_mtx",
+    "tf_multi_exec", "tf_multi_status", "tf_multi_trace", "tf_partition_layout", "tf_read_matrix", "tf_read_dense_mtx",
     "tf_schedule_unfused_csr", "tf_schedule_reordered_adj", "tf_rcm_order", "tf_permute_csr",
 ]
 
@@ -119,6 +119,7 @@ def lib() -> C.CDLL:
     L.tf_multi_plan_handle.restype = vp
     L.tf_multi_exec.argtypes = [vp, vp, vp, i, i, vp, vp]
     L.tf_multi_status.argtypes = [vp, vp]
+    L.tf_multi_trace.argtypes = [vp, C.c_int, C.POINTER(C.c_float)]
     L.tf_partition_layout.argtypes = [i, i, vp, vp, vp, C.POINTER(vp), C.POINTER(ll), C.POINTER(vp), ip, C.POINTER(vp), ip]
     L.tf_schedule_unfused_csr.argtypes = [vp, i, vp, vp, vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), ip]
     L.tf_schedule_reordered_adj.argtypes = [vp, i, vp, vp, vp] + [C.POINTER(vp)] * 5 + [ip]

@@ -8,11 +8,15 @@
 //     of T with those ids arrive from their owners and are stored after the local rows;
 //   * its boundary is the sorted list of its own rows that appear in some other rank's halo; they are
 //     produced first (phase 0) into a send buffer laid out in that order.
-// Only halo rows of T travel (ncclSend / ncclRecv in one group on a second stream); the exchange overlaps
-// phase 1, the rows that need no halo row.  NCCL is resolved at run time from the process (libnccl.so.2),
-// so the library has no link-time dependency on it.
+// Only halo rows of T travel, on a second stream, beside phase 1 (the rows that need no halo row).  Where every
+// rank is a process of its own on one host, the copy engines write the send segments over NVLink straight into
+// the neighbours' halo rows (mapped through CUDA IPC) and NCCL carries one-int tokens around the copies; else
+// the rows go through ncclSend / ncclRecv in one group.  The communicator is created with at most four CTAs per
+// NCCL kernel, so that those kernels fit on the SMs the persistent kernel of phase 1 leaves free.  NCCL is resolved
+// at run time from the process (libnccl.so.2), so the library has no link-time dependency on it.
 #include <cuda_runtime.h>
 #include <dlfcn.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <climits>
@@ -138,7 +142,7 @@ struct Nccl {
   const char *(*GetErrorString)(int) = nullptr;
   bool ok = false;
 };
-constexpr int kNcclInt8 = 0, kNcclFloat = 7;  // ncclInt8 / ncclChar, ncclFloat32
+constexpr int kNcclInt8 = 0, kNcclInt32 = 2, kNcclFloat = 7;  // ncclInt8 / ncclChar, ncclInt32, ncclFloat32
 
 Nccl &nccl() {
   static Nccl n;
@@ -201,14 +205,125 @@ struct tf_multi {
   std::vector<Gather> gathers;  // per send segment (null when the segment is contiguous)
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t ready = nullptr, arrived = nullptr;
+  // Direct exchange (every rank a process of its own on one host, peer access between the GPUs): the send segments
+  // are copied by the copy engines straight into the neighbours' halo rows, whose allocations are mapped here
+  // through CUDA IPC; NCCL only carries one-int tokens.  Empty: the rows travel through ncclSend / ncclRecv.
+  bool direct = false;
+  std::vector<void *> peer_base;   // per send segment: the peer's mapped allocation (to be closed)
+  std::vector<float *> peer_dst;   // per send segment: where its rows go in the peer's halo rows
+  int *tokens = nullptr;           // device: [0] the token sent, [1 ..] tokens received
+  // timing of the last step (tf_multi_trace): start, phase 0 done, exchange done, phase 2 done, phase 1 done, end
+  bool trace = false;
+  cudaEvent_t tev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   ~tf_multi() {
     for (auto &g : gathers) { if (g.idx) cudaFree(g.idx); if (g.stage) cudaFree(g.stage); }
+    for (void *b : peer_base) if (b) cudaIpcCloseMemHandle(b);
+    if (tokens) cudaFree(tokens);
     if (plan) tf_plan_free(plan);
     if (ready) cudaEventDestroy(ready);
     if (arrived) cudaEventDestroy(arrived);
+    for (cudaEvent_t e : tev) if (e) cudaEventDestroy(e);
     if (comm_stream) cudaStreamDestroy(comm_stream);
   }
 };
+
+namespace {
+
+struct ExchangeCard {   // what a rank tells the others about its halo rows
+  cudaIpcMemHandle_t handle;   // of the allocation that holds them
+  long long halo_offset;       // bytes from the allocation's start to the first halo row
+  long long host, pid;
+  int has_halo, pad;
+};
+
+// all-gather of one fixed-size record per rank through a device buffer
+template <class T>
+int gather_records(tf_multi &M, const T &mine, std::vector<T> &all) {
+  const int world = M.c->world, rank = M.c->rank;
+  all.resize(world);
+  char *d = nullptr;
+  TF_CUDA(cudaMalloc(&d, sizeof(T) * (size_t)world));
+  TF_CUDA(cudaMemcpy(d + sizeof(T) * rank, &mine, sizeof(T), cudaMemcpyHostToDevice));
+  TF_NCCL(nccl().AllGather(d + sizeof(T) * rank, d, sizeof(T), kNcclInt8, M.c->comm, M.comm_stream));
+  TF_CUDA(cudaStreamSynchronize(M.comm_stream));
+  TF_CUDA(cudaMemcpy(all.data(), d, sizeof(T) * (size_t)world, cudaMemcpyDeviceToHost));
+  cudaFree(d);
+  return TF_OK;
+}
+
+// Collective.  Maps the neighbours' halo rows into this process where that is possible; the direct exchange is
+// used only if every rank could map all it needs (TF_EXCHANGE=nccl in the environment keeps ncclSend / ncclRecv).
+int setup_direct_exchange(tf_multi &M, const std::vector<long long> &bounds, const std::vector<std::vector<long long>> &halos) {
+  const int world = M.c->world, rank = M.c->rank;
+  if (world < 2) return TF_OK;
+  ExchangeCard me;
+  std::memset(&me, 0, sizeof(me));
+  char host[256] = {0};
+  gethostname(host, sizeof(host) - 1);
+  for (const char *q = host; *q; ++q) me.host = me.host * 131 + (unsigned char)*q;
+  me.pid = (long long)getpid();
+  float *base = nullptr;
+  long long rows = 0;
+  int cols = 0;
+  int rc = tf_plan_intermediate(M.plan, &base, &rows, &cols);
+  if (rc != TF_OK) return rc;
+  const char *env = getenv("TF_EXCHANGE");
+  bool can = !(env && std::strcmp(env, "nccl") == 0);
+  if (M.halobuf && base) {
+    me.has_halo = 1;
+    me.halo_offset = (long long)((const char *)M.halobuf - (const char *)base);
+    if (cudaIpcGetMemHandle(&me.handle, base) != cudaSuccess) { (void)cudaGetLastError(); can = false; }
+  }
+  std::vector<ExchangeCard> cards;
+  rc = gather_records(M, me, cards);
+  if (rc != TF_OK) return rc;
+  const tf::RankLayout &lay = M.lay;
+  M.peer_base.assign(lay.send.size(), nullptr);
+  M.peer_dst.assign(lay.send.size(), nullptr);
+  for (size_t i = 0; i < lay.send.size() && can; ++i) {
+    const int q = lay.send[i].peer;
+    const ExchangeCard &cq = cards[q];
+    if (!cq.has_halo || cq.host != me.host || cq.pid == me.pid) { can = false; break; }
+    tf::RankLayout lq;   // where the peer expects this rank's rows
+    tf::make_layout(q, world, bounds.data(), halos, lq);
+    long long start = -1;
+    for (const tf::ExchangeSegment &r : lq.recv)
+      if (r.peer == rank && r.count == lay.send[i].count) start = r.start;
+    if (start < 0) { can = false; break; }
+    void *mapped = nullptr;
+    if (cudaIpcOpenMemHandle(&mapped, cq.handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+      (void)cudaGetLastError();
+      can = false;
+      break;
+    }
+    M.peer_base[i] = mapped;
+    M.peer_dst[i] = reinterpret_cast<float *>((char *)mapped + cq.halo_offset) + (size_t)start * M.n_cols;
+  }
+  std::vector<int> votes;
+  rc = gather_records(M, (int)can, votes);
+  if (rc != TF_OK) return rc;
+  for (int v : votes) can = can && v != 0;
+  if (!can) {
+    for (void *&b : M.peer_base) if (b) { cudaIpcCloseMemHandle(b); b = nullptr; }
+    M.peer_base.clear(); M.peer_dst.clear();
+    return TF_OK;
+  }
+  TF_CUDA(cudaMalloc(&M.tokens, sizeof(int) * (2 + (size_t)world)));
+  TF_CUDA(cudaMemset(M.tokens, 0, sizeof(int) * (2 + (size_t)world)));
+  M.direct = true;
+  return TF_OK;
+}
+
+// One-int messages between neighbours in one NCCL group: this rank sends to `to`, receives from `from`.
+int token_round(tf_multi &M, const std::vector<int> &to, const std::vector<int> &from) {
+  TF_NCCL(nccl().GroupStart());
+  for (int q : to) TF_NCCL(nccl().Send(M.tokens, 1, kNcclInt32, q, M.c->comm, M.comm_stream));
+  for (size_t i = 0; i < from.size(); ++i) TF_NCCL(nccl().Recv(M.tokens + 1 + i, 1, kNcclInt32, from[i], M.c->comm, M.comm_stream));
+  TF_NCCL(nccl().GroupEnd());
+  return TF_OK;
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -358,6 +473,8 @@ int tf_multi_plan(tf_comm *c, int chain, long long r0, long long r1, const int *
     TF_CUDA(cudaMemcpy(M->gathers[i].idx, lay.send[i].index.data(), sizeof(long long) * lay.send[i].index.size(), cudaMemcpyHostToDevice));
     TF_CUDA(cudaMalloc(&M->gathers[i].stage, sizeof(float) * lay.send[i].index.size() * n_cols));
   }
+  rc = setup_direct_exchange(*M, bounds, halos);
+  if (rc != TF_OK) return rc;
   *out = M.release();
   return TF_OK;
 }
@@ -391,11 +508,14 @@ int tf_multi_exec(tf_multi *m, const float *in0, const float *in1, int w_transpo
   tf_plan_info(m->plan, pinfo);
   const bool marching = pinfo[5] == 128 && m->chain == 0;
   const bool exchange = !lay.send.empty() || !lay.recv.empty();
+  const bool tr = m->trace;
+  if (tr) TF_CUDA(cudaEventRecord(m->tev[0], s));
   // Phase 0 (the boundary rows for the neighbours) is short and goes first, on every SM.
   if (!lay.boundary_rows.empty()) {
     rc = tf_exec_phase(m->plan, 0, in0, in1, w_transposed, relu, nullptr, s);
     if (rc != TF_OK) return rc;
   }
+  if (tr) TF_CUDA(cudaEventRecord(m->tev[1], s));
   if (exchange) {
     TF_CUDA(cudaEventRecord(m->ready, s));
     TF_CUDA(cudaStreamWaitEvent(m->comm_stream, m->ready, 0));
@@ -405,16 +525,35 @@ int tf_multi_exec(tf_multi *m, const float *in0, const float *in1, int w_transpo
             m->sendbuf, m->gathers[i].idx, lay.send[i].count, m->n_cols, m->gathers[i].stage);
         TF_CUDA(cudaGetLastError());
       }
-    TF_NCCL(nccl().GroupStart());
-    for (size_t i = 0; i < lay.send.size(); ++i) {
-      const float *src = m->gathers[i].idx ? m->gathers[i].stage : m->sendbuf + (size_t)lay.send[i].start * m->n_cols;
-      TF_NCCL(nccl().Send(src, (size_t)lay.send[i].count * m->n_cols, kNcclFloat, lay.send[i].peer, m->c->comm, m->comm_stream));
+    if (m->direct) {
+      // (1) every rank tells the ranks that write into its halo rows that its previous step no longer reads them,
+      // (2) the copy engines move the send segments into the neighbours' halo rows, (3) every rank tells the
+      // owners of those rows that they are complete.  No SM moves data; the two token kernels are one CTA each.
+      std::vector<int> senders, receivers;
+      for (const tf::ExchangeSegment &r : lay.recv) senders.push_back(r.peer);
+      for (const tf::ExchangeSegment &x : lay.send) receivers.push_back(x.peer);
+      rc = token_round(*m, senders, receivers);
+      if (rc != TF_OK) return rc;
+      for (size_t i = 0; i < lay.send.size(); ++i) {
+        const float *src = m->gathers[i].idx ? m->gathers[i].stage : m->sendbuf + (size_t)lay.send[i].start * m->n_cols;
+        TF_CUDA(cudaMemcpyAsync(m->peer_dst[i], src, sizeof(float) * (size_t)lay.send[i].count * m->n_cols, cudaMemcpyDeviceToDevice,
+                                m->comm_stream));
+      }
+      rc = token_round(*m, receivers, senders);
+      if (rc != TF_OK) return rc;
+    } else {
+      TF_NCCL(nccl().GroupStart());
+      for (size_t i = 0; i < lay.send.size(); ++i) {
+        const float *src = m->gathers[i].idx ? m->gathers[i].stage : m->sendbuf + (size_t)lay.send[i].start * m->n_cols;
+        TF_NCCL(nccl().Send(src, (size_t)lay.send[i].count * m->n_cols, kNcclFloat, lay.send[i].peer, m->c->comm, m->comm_stream));
+      }
+      for (const tf::ExchangeSegment &r : lay.recv)
+        TF_NCCL(nccl().Recv(m->halobuf + (size_t)r.start * m->n_cols, (size_t)r.count * m->n_cols, kNcclFloat, r.peer, m->c->comm,
+                            m->comm_stream));
+      TF_NCCL(nccl().GroupEnd());
     }
-    for (const tf::ExchangeSegment &r : lay.recv)
-      TF_NCCL(nccl().Recv(m->halobuf + (size_t)r.start * m->n_cols, (size_t)r.count * m->n_cols, kNcclFloat, r.peer, m->c->comm,
-                          m->comm_stream));
-    TF_NCCL(nccl().GroupEnd());
     TF_CUDA(cudaEventRecord(m->arrived, m->comm_stream));
+    if (tr) TF_CUDA(cudaEventRecord(m->tev[2], m->comm_stream));
   }
   if (marching && exchange) {
     // Plane-marching plans compute the intermediate inside phase 1, which therefore does not wait for anything.
@@ -424,15 +563,43 @@ int tf_multi_exec(tf_multi *m, const float *in0, const float *in1, int w_transpo
     rc = tf_exec_phase(m->plan, 2, in0, in1, w_transposed, relu, D, m->comm_stream);
     if (rc != TF_OK) return rc;
     TF_CUDA(cudaEventRecord(m->arrived, m->comm_stream));
+    if (tr) TF_CUDA(cudaEventRecord(m->tev[3], m->comm_stream));
     rc = tf_exec_phase(m->plan, 1, in0, in1, w_transposed, relu, D, s);
     if (rc != TF_OK) return rc;
+    if (tr) TF_CUDA(cudaEventRecord(m->tev[4], s));
     TF_CUDA(cudaStreamWaitEvent(s, m->arrived, 0));
+    if (tr) TF_CUDA(cudaEventRecord(m->tev[5], s));
     return TF_OK;
   }
   rc = tf_exec_phase(m->plan, 1, in0, in1, w_transposed, relu, D, s);
   if (rc != TF_OK) return rc;
+  if (tr) TF_CUDA(cudaEventRecord(m->tev[4], s));
   if (exchange) TF_CUDA(cudaStreamWaitEvent(s, m->arrived, 0));
-  return tf_exec_phase(m->plan, 2, in0, in1, w_transposed, relu, D, s);
+  rc = tf_exec_phase(m->plan, 2, in0, in1, w_transposed, relu, D, s);
+  if (tr) {
+    TF_CUDA(cudaEventRecord(m->tev[3], s));
+    TF_CUDA(cudaEventRecord(m->tev[5], s));
+  }
+  return rc;
+}
+
+// on != 0: the following steps record their phases; ms (may be null) receives the times of the last traced step,
+// measured from its start: {phase 0 done, exchange done, phase 2 done, phase 1 done, step done} (-1: not recorded).
+int tf_multi_trace(tf_multi *m, int on, float ms[5]) {
+  if (!m) return fail(TF_ERR_ARG, "tf_multi_trace: null argument");
+  TF_CUDA(cudaSetDevice(m->c->device));
+  if (ms) {
+    for (int i = 0; i < 5; ++i) ms[i] = -1.f;
+    if (m->trace && m->tev[0]) {
+      TF_CUDA(cudaDeviceSynchronize());
+      for (int i = 1; i < 6; ++i)
+        if (cudaEventElapsedTime(&ms[i - 1], m->tev[0], m->tev[i]) != cudaSuccess) { ms[i - 1] = -1.f; (void)cudaGetLastError(); }
+    }
+  }
+  if (on && !m->tev[0])
+    for (cudaEvent_t &e : m->tev) TF_CUDA(cudaEventCreate(&e));
+  m->trace = on != 0;
+  return TF_OK;
 }
 
 int tf_multi_status(tf_multi *m, void *stream) {

@@ -152,6 +152,17 @@ class NativeRankChain:
         from .api import _stream_ptr
         _lib.check(_lib.lib().tf_multi_status(self._h, stream if stream is not None else _stream_ptr()))
 
+    def trace(self, on=True):
+        """Switches step tracing on / off and returns the last traced step's times (ms from its start) as a dict,
+        or None when no traced step has run."""
+        import ctypes
+        from . import _lib
+        ms = (ctypes.c_float * 5)()
+        _lib.check(_lib.lib().tf_multi_trace(self._h, int(bool(on)), ms))
+        if ms[4] < 0:
+            return None
+        return dict(zip(("phase0_done", "exchange_done", "phase2_done", "phase1_done", "step_done"), (float(v) for v in ms)))
+
     def close(self):
         from . import _lib
         if getattr(self, "_h", None):
