@@ -148,6 +148,10 @@ struct tf_plan {
     int first_idle_sm = INT_MAX;
     DevBuf<tfk::MarchState> st;   // [0]: tickets of phase 1 (or of the whole grid), [1]: of phase 2 -- the two may run side by side
     std::vector<tf::MarchItem> host_items;
+    // host-pointer path (single GPU): the grid again, cut into slabs of planes that run one launch each while the
+    // planes of C for the next slab arrive and the planes of D of the one before leave
+    struct Slab { int item_begin, item_end, z_begin, z_end; };
+    std::vector<Slab> slabs;
   } march;
   // schedule mode
   DevBuf<int> s_ptr2, s_id, s_type, s_ker;
@@ -335,13 +339,22 @@ int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int halo_rows, int
   if (M.halo_lo) tf::build_march_items(M.nx, M.ny, 0, 1, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, M.grid, 1, M.host_items);
   if (M.halo_hi && M.nz > 1)
     tf::build_march_items(M.nx, M.ny, M.nz - 1, M.nz, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, M.grid, 1, M.host_items);
+  M.n_items = (int)M.host_items.size();
+  if (halo_rows == 0 && M.nz >= 8) {
+    const int n_slabs = std::min(32, M.nz / 4);
+    for (int sl = 0; sl < n_slabs; ++sl) {
+      const int za = (int)((long long)M.nz * sl / n_slabs), zb = (int)((long long)M.nz * (sl + 1) / n_slabs);
+      const int b = (int)M.host_items.size();
+      tf::build_march_items(M.nx, M.ny, za, zb, p.n_cols, tfk::kMarchW, tfk::kMarchH, tfk::kMarchCols, M.grid, 1, M.host_items);
+      M.slabs.push_back(tf_plan::March::Slab{b, (int)M.host_items.size(), za, zb});
+    }
+  }
   std::vector<int4> raw(2 * M.host_items.size());
   for (size_t i = 0; i < M.host_items.size(); ++i) {
     const tf::MarchItem &it = M.host_items[i];
     raw[2 * i] = make_int4(it.x0, it.y0, it.zs, it.ze);
     raw[2 * i + 1] = make_int4(it.c0, it.flags, 0, 0);
   }
-  M.n_items = (int)M.host_items.size();
   rc = M.items.upload(raw);
   if (rc == TF_OK) rc = M.pcls_f.upload(lf.patch_cls);
   M.dict_f = lf.dict;
@@ -748,6 +761,49 @@ int run_host_pipeline(tf_plan &p, tfk::Params &P, const float *h_in, long long i
   return TF_OK;
 }
 
+// The same pipeline for plane-marching plans: one launch per slab of planes.  A slab [za, zb) reads the planes
+// za - 2 .. zb + 1 of C and completes the planes [za, zb) of D, so the copies run two planes ahead of the kernel
+// and the output leaves slab by slab.
+int run_host_march(tf_plan &p, const float *h_in, float *d_in, float *h_out, float *d_out) {
+  tf_plan::March &M = p.march;
+  if (!p.s_h2d) {
+    TF_CUDA(cudaStreamCreateWithFlags(&p.s_h2d, cudaStreamNonBlocking));
+    TF_CUDA(cudaStreamCreateWithFlags(&p.s_run, cudaStreamNonBlocking));
+    TF_CUDA(cudaStreamCreateWithFlags(&p.s_d2h, cudaStreamNonBlocking));
+  }
+  const int ns = (int)M.slabs.size();
+  while ((int)p.ev_in.size() < ns) {
+    cudaEvent_t a, b;
+    TF_CUDA(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+    TF_CUDA(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+    p.ev_in.push_back(a); p.ev_run.push_back(b);
+  }
+  const size_t plane = (size_t)M.nx * M.ny * p.n_cols;
+  int planes_in = 0;
+  long long launches = 0;
+  for (int sl = 0; sl < ns; ++sl) {
+    const tf_plan::March::Slab &g = M.slabs[sl];
+    const int need = std::min(M.nz, g.z_end + 2);
+    if (need > planes_in)
+      TF_CUDA(cudaMemcpyAsync(d_in + plane * planes_in, h_in + plane * planes_in, plane * (size_t)(need - planes_in) * sizeof(float),
+                              cudaMemcpyHostToDevice, p.s_h2d));
+    planes_in = std::max(planes_in, need);
+    TF_CUDA(cudaEventRecord(p.ev_in[sl], p.s_h2d));
+    TF_CUDA(cudaStreamWaitEvent(p.s_run, p.ev_in[sl], 0));
+    int rc = run_march(p, d_in, d_out, g.item_begin, g.item_end, false, p.s_run);
+    if (rc != TF_OK) return rc;
+    launches += p.launches;
+    TF_CUDA(cudaEventRecord(p.ev_run[sl], p.s_run));
+    TF_CUDA(cudaStreamWaitEvent(p.s_d2h, p.ev_run[sl], 0));
+    TF_CUDA(cudaMemcpyAsync(h_out + plane * g.z_begin, d_out + plane * g.z_begin, plane * (size_t)(g.z_end - g.z_begin) * sizeof(float),
+                            cudaMemcpyDeviceToHost, p.s_d2h));
+  }
+  p.launches = launches;
+  TF_CUDA(cudaStreamSynchronize(p.s_d2h));
+  TF_CUDA(cudaStreamSynchronize(p.s_run));
+  return TF_OK;
+}
+
 int run_unfused(tf_plan &p, tfk::Params &P, cudaStream_t s) {
   // all producers are listed before all consumers: one launch per half, T through HBM
   int vec, ch;
@@ -985,6 +1041,17 @@ int tf_spmm_spmm_host(tf_plan *p, const float *C, float *D) {
   int rc = set_device(*p);
   if (rc != TF_OK) return rc;
   const size_t nd = (size_t)p->m * p->n_cols;
+  if (!p->march.slabs.empty()) {
+    const size_t nin = (size_t)p->first_cols * p->n_cols;
+    if (p->h_in0.n < nin) rc = p->h_in0.alloc(nin);
+    if (rc == TF_OK && p->h_out.n < nd) rc = p->h_out.alloc(nd);
+    if (rc != TF_OK) return rc;
+    if (march_usable(*p, p->h_in0.p, p->h_out.p)) {
+      rc = run_host_march(*p, C, p->h_in0.p, D, p->h_out.p);
+      if (rc != TF_OK) return rc;
+      return tf_plan_status(p, nullptr);
+    }
+  }
   if (p->segs.size() > 1) {
     const size_t nin = (size_t)p->first_cols * p->n_cols;
     if (p->h_in0.n < nin) rc = p->h_in0.alloc(nin);
