@@ -50,9 +50,9 @@ WORKLOADS = {
                label="GeMM-SpMM fp32 D=A*(B*C), 3-D 7-pt Laplacian 256^3 (whole job), B n x 256, C 256 x 256"),
 }
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
-# summarised under profiles/ (captured on a quarter-size case and scaled by rows)
-DRAM_TRAFFIC = {"c2": 4 * (316_122_368 + 231_768_576)}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on the full workload, from
+# the ncu capture summarised in profiles/lattice_march_kernel_spmm_spmm_laplacian3d.md
+DRAM_TRAFFIC = {"c2": 1_207_925_000 + 1_040_525_000}
 
 # TileM values (bytes of cache per tile) of the reference's own sweep, fusion/scripts/run_exp.sh mode 7, thinned
 TILE_M_SWEEP = (60_000, 300_000, 1_250_000)

@@ -134,6 +134,11 @@ def test_plane_march_shapes(torch_cuda, oracle, dims, n_cols):
         ref_plan.spmm_spmm(cd, d0)
         ref_plan.status()
         assert torch.equal(d, d0), what
+        # the host-pointer call of the same plan (grids of 8 planes or more: one launch per slab of planes between
+        # the copy streams) must give the same bits
+        dh = np.full((n, n_cols), np.nan, np.float32)
+        plan.spmm_spmm_host(c, dh)
+        assert np.array_equal(dh, d.cpu().numpy()), what + " (host pointers)"
         plan.close()
         ref_plan.close()
 
