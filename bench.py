@@ -2,7 +2,7 @@
 """Benchmark of the fused sparse-dense chains on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c5|c3|c4] [--impl ours|reference]
-                    [--mode stream|unfused] [--quick]
+                    [--mode stream|unfused] [--quick] [--dims X,Y,Z]
 
 A step is one pass of the fused chain over one resident batch of synthetic input.  The headline workload
 is the SpMM-SpMM chain D = A*(A*C) on the 3-D 7-point Laplacian of a 128^3 grid with 128 dense columns
@@ -405,7 +405,9 @@ def run_lattice_workload(name, args, ctx, headline):
     wl = WORKLOADS[name]
     chain, n = wl["chain"], wl["n"]
     k = wl.get("k", 0)
-    dims = list(wl["dims"])
+    dims = [int(v) for v in args.dims.split(",")] if args.dims else list(wl["dims"])
+    if len(dims) != len(wl["dims"]):
+        raise SystemExit(f"--dims: workload {name} has a {len(wl['dims'])}-D grid")
     strong = wl["scaling"] == "strong"
     if not strong and world > 1:
         dims[-1] *= world  # weak scaling: the grid grows along its slowest axis
@@ -519,7 +521,7 @@ def run_lattice_workload(name, args, ctx, headline):
                 "traffic": None, "peak_source": f"of {peak_kind}", "algorithmic_bytes_per_launch": bytes_local,
                 "kernel": kernel + " (persistent fused executor)", "kernel_ms": kernel_ms,
                 "kernel_ms_min": float(np.min(per_step))}
-    if world == 1 and args.mode == "stream" and name in DRAM_TRAFFIC and kernel == "lattice_march_kernel":
+    if world == 1 and args.mode == "stream" and name in DRAM_TRAFFIC and kernel == "lattice_march_kernel" and not args.dims:
         roofline["traffic"] = DRAM_TRAFFIC[name]
     if chain == "gemm_spmm" and rank == 0:
         # the dense producer multiplies three TF32 products per fp32 product: its floor is a tensor-core time
@@ -616,7 +618,8 @@ def run_lattice_workload(name, args, ctx, headline):
     return {"metric": METRICS[chain], "value": value, "unit": UNIT, "n_gpus": world, "steps": steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": wl["scaling"], "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl["label"], "grid": "x".join(map(str, dims)), "rows": n_rows,
+            "config": {"workload": wl["label"] + (" -- grid overridden by --dims (a profiling case)" if args.dims else ""),
+                       "grid": "x".join(map(str, dims)), "rows": n_rows,
                        "rows_per_gpu": m, "mode": args.mode, "ring_rows": info["ring_rows"], "grid_ctas": info["grid"],
                        "threads_per_cta": threads, "tiles": tiles, "setup_s": round(setup_s, 1),
                        "l2": "inputs (>= 1 GB per step) exceed the 126 MB L2; no flush" if bytes_local > 5e8 else
@@ -636,6 +639,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="stream", choices=["stream", "unfused"])
     ap.add_argument("--quick", action="store_true", help="kernel timing only: no CPU baseline, no 'also' workloads")
+    ap.add_argument("--dims", default="", help="grid of a lattice workload, e.g. 128,128,32: a small case of the same kernel "
+                                               "for profiler captures (the line then names that grid, not the workload's)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
