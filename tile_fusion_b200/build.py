@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 LIB = os.path.join(HERE, "libtilefusion_b200.so")
 SOURCES = ["kernels.cu", "api.cu", "inspector.cpp", "planner.cpp", "tiling.cpp", "noalloc.cu", "gemm_tc.cu", "tile_pipeline.cu", "lattice.cpp", "lattice_march.cu", "multi.cu", "io.cpp", "reorder.cpp"]
-HEADERS = ["kernels.cuh", "launch.h", "tf_internal.h", "gemm_tc.cuh", "gemm_tc_host.h", "lattice_march.h"]
+HEADERS = ["kernels.cuh", "launch.h", "tf_internal.h", "gemm_tc.cuh", "gemm_tc_host.h", "lattice_march.h", "host_stage.h"]
 
 
 def _stale() -> bool:
