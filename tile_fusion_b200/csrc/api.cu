@@ -167,7 +167,7 @@ struct tf_plan {
   std::vector<Seg> segs;
   cudaStream_t s_h2d = nullptr, s_run = nullptr, s_d2h = nullptr;
   std::vector<cudaEvent_t> ev_in, ev_run;
-  std::unique_ptr<tf::StageRings> rings;   // pinned slots for pageable arrays (host_stage.h)
+  std::unique_ptr<tf::HostPipe> host_pipe;   // copies of the host-pointer calls; pinned slots for pageable arrays (host_stage.h)
   ~tf_plan() {
     for (cudaEvent_t e : ev_in) cudaEventDestroy(e);
     for (cudaEvent_t e : ev_run) cudaEventDestroy(e);
@@ -705,6 +705,16 @@ void build_segments(tf_plan &p, int n_seg) {
   }
 }
 
+// Copies of one host-pointer call: plain for pinned arrays, through the pinned rings for pageable ones.
+int begin_host_pipe(tf_plan &p, const void *h_in, const void *h_out) {
+  if (!p.host_pipe) {
+    const int t = (int)std::min(8u, std::max(2u, std::thread::hardware_concurrency() / 2));
+    p.host_pipe.reset(new tf::HostPipe(t));
+  }
+  TF_CUDA(p.host_pipe->begin(p.device, tf::is_pageable(h_in), tf::is_pageable(h_out), (size_t)8 << 20, 16));
+  return TF_OK;
+}
+
 // Host pipeline: the dense input is copied in row chunks on one stream, the item list runs in segments
 // on a second as soon as the rows a segment reads have arrived, and finished output rows leave on a
 // third.  in_rows x in_cols floats come from h_in; D is m x n_cols.
@@ -727,6 +737,8 @@ int run_host_pipeline(tf_plan &p, tfk::Params &P, const float *h_in, long long i
   if (p.dyn_smem > 0) { vec = 4; ch = 1; }
   int rc = prepare_tc(p, P, p.s_run);
   if (rc != TF_OK) return rc;
+  rc = begin_host_pipe(p, h_in, h_out);
+  if (rc != TF_OK) return rc;
   const bool ring = p.hp.ring_rows > 0;
   ++p.epoch;
   P.epoch = p.epoch;
@@ -738,8 +750,7 @@ int run_host_pipeline(tf_plan &p, tfk::Params &P, const float *h_in, long long i
     const tf_plan::Seg &g = p.segs[s];
     const long long in_to = s == ns - 1 ? in_rows : std::min(in_rows, g.in_rows);
     if (in_to > in_done)
-      TF_CUDA(cudaMemcpyAsync(d_in + in_done * in_cols, h_in + in_done * in_cols, (size_t)(in_to - in_done) * in_cols * 4,
-                              cudaMemcpyHostToDevice, p.s_h2d));
+      TF_CUDA(p.host_pipe->upload(d_in + in_done * in_cols, h_in + in_done * in_cols, (size_t)(in_to - in_done) * in_cols * 4, p.s_h2d));
     in_done = std::max(in_done, in_to);
     TF_CUDA(cudaEventRecord(p.ev_in[s], p.s_h2d));
     TF_CUDA(cudaStreamWaitEvent(p.s_run, p.ev_in[s], 0));
@@ -756,11 +767,12 @@ int run_host_pipeline(tf_plan &p, tfk::Params &P, const float *h_in, long long i
     const long long out_to = s == ns - 1 ? p.m : g.out_rows;
     if (out_to > out_done) {
       TF_CUDA(cudaStreamWaitEvent(p.s_d2h, p.ev_run[s], 0));
-      TF_CUDA(cudaMemcpyAsync(h_out + out_done * p.n_cols, d_out + out_done * p.n_cols,
-                              (size_t)(out_to - out_done) * p.n_cols * 4, cudaMemcpyDeviceToHost, p.s_d2h));
+      TF_CUDA(p.host_pipe->download(h_out + out_done * p.n_cols, d_out + out_done * p.n_cols,
+                               (size_t)(out_to - out_done) * p.n_cols * 4, p.s_d2h));
       out_done = out_to;
     }
   }
+  TF_CUDA(p.host_pipe->finish());
   TF_CUDA(cudaStreamSynchronize(p.s_d2h));
   TF_CUDA(cudaStreamSynchronize(p.s_run));
   return TF_OK;
@@ -768,8 +780,8 @@ int run_host_pipeline(tf_plan &p, tfk::Params &P, const float *h_in, long long i
 
 // The same pipeline for plane-marching plans: one launch per slab of planes.  A slab [za, zb) reads the planes
 // za - 2 .. zb + 1 of C and completes the planes [za, zb) of D, so the copies run two planes ahead of the kernel
-// and the output leaves slab by slab.  Pageable arrays go plane by plane through rings of pinned slots
-// (host_stage.h): this thread fills the upload slots, a second one empties the download slots.
+// and the output leaves slab by slab.  Pageable arrays go piece by piece through rings of pinned slots
+// (host_stage.h).
 int run_host_march(tf_plan &p, const float *h_in, float *d_in, float *h_out, float *d_out) {
   tf_plan::March &M = p.march;
   if (!p.s_h2d) {
@@ -785,108 +797,27 @@ int run_host_march(tf_plan &p, const float *h_in, float *d_in, float *h_out, flo
     p.ev_in.push_back(a); p.ev_run.push_back(b);
   }
   const size_t plane = (size_t)M.nx * M.ny * p.n_cols, plane_bytes = plane * sizeof(float);
-  bool stage_in = tf::is_pageable(h_in), stage_out = tf::is_pageable(h_out);
-  tf::StageRings *R = nullptr;
-  if ((stage_in || stage_out) && plane_bytes <= ((size_t)64 << 20)) {
-    if (!p.rings) {
-      const int t = (int)std::min(8u, std::max(2u, std::thread::hardware_concurrency() / 2));
-      p.rings.reset(new tf::StageRings(t, t));
-    }
-    const int slots = (int)std::min<size_t>(32, std::max<size_t>(4, ((size_t)128 << 20) / plane_bytes));
-    TF_CUDA(p.rings->reserve(plane_bytes, slots));
-    R = p.rings.get();
-  } else {
-    stage_in = stage_out = false;   // pinned arrays, or planes too large for the rings: plain copies
-  }
-
-  // download side: planes whose copy into a slot has been enqueued / that have reached the caller's array
-  struct Drain {
-    std::mutex m;
-    std::condition_variable cv;
-    int issued = 0, drained = 0;
-    bool stop = false, failed = false;
-    std::thread th;
-    ~Drain() {
-      { std::lock_guard<std::mutex> g(m); stop = true; }
-      cv.notify_all();
-      if (th.joinable()) th.join();
-    }
-  } drain;
-  if (stage_out) {
-    const int device = p.device, nz = M.nz;
-    drain.th = std::thread([&drain, R, h_out, plane, plane_bytes, device, nz] {
-      cudaSetDevice(device);
-      for (int q = 0; q < nz; ++q) {
-        {
-          std::unique_lock<std::mutex> g(drain.m);
-          drain.cv.wait(g, [&] { return drain.issued > q || drain.stop; });
-          if (drain.issued <= q) return;
-        }
-        const int slot = q % R->slots;
-        if (cudaEventSynchronize(R->out_landed[slot]) != cudaSuccess) {
-          std::lock_guard<std::mutex> g(drain.m);
-          drain.failed = true; drain.drained = nz;
-          drain.cv.notify_all();
-          return;
-        }
-        R->crew_out.copy(h_out + plane * q, R->out + (size_t)slot * plane_bytes, plane_bytes);
-        { std::lock_guard<std::mutex> g(drain.m); drain.drained = q + 1; }
-        drain.cv.notify_all();
-      }
-    });
-  }
-
+  int rc = begin_host_pipe(p, h_in, h_out);
+  if (rc != TF_OK) return rc;
   int planes_in = 0;
   long long launches = 0;
   for (int sl = 0; sl < ns; ++sl) {
     const tf_plan::March::Slab &g = M.slabs[sl];
     const int need = std::min(M.nz, g.z_end + 2);
-    if (need > planes_in) {
-      if (stage_in) {
-        for (int q = planes_in; q < need; ++q) {
-          const int slot = q % R->slots;
-          if (q >= R->slots) TF_CUDA(cudaEventSynchronize(R->in_sent[slot]));
-          R->crew_in.copy(R->in + (size_t)slot * plane_bytes, h_in + plane * q, plane_bytes);
-          TF_CUDA(cudaMemcpyAsync(d_in + plane * q, R->in + (size_t)slot * plane_bytes, plane_bytes, cudaMemcpyHostToDevice, p.s_h2d));
-          TF_CUDA(cudaEventRecord(R->in_sent[slot], p.s_h2d));
-        }
-      } else {
-        TF_CUDA(cudaMemcpyAsync(d_in + plane * planes_in, h_in + plane * planes_in, plane_bytes * (size_t)(need - planes_in),
-                                cudaMemcpyHostToDevice, p.s_h2d));
-      }
-    }
+    if (need > planes_in)
+      TF_CUDA(p.host_pipe->upload(d_in + plane * planes_in, h_in + plane * planes_in, plane_bytes * (size_t)(need - planes_in), p.s_h2d));
     planes_in = std::max(planes_in, need);
     TF_CUDA(cudaEventRecord(p.ev_in[sl], p.s_h2d));
     TF_CUDA(cudaStreamWaitEvent(p.s_run, p.ev_in[sl], 0));
-    int rc = run_march(p, d_in, d_out, g.item_begin, g.item_end, false, p.s_run);
+    rc = run_march(p, d_in, d_out, g.item_begin, g.item_end, false, p.s_run);
     if (rc != TF_OK) return rc;
     launches += p.launches;
     TF_CUDA(cudaEventRecord(p.ev_run[sl], p.s_run));
     TF_CUDA(cudaStreamWaitEvent(p.s_d2h, p.ev_run[sl], 0));
-    if (stage_out) {
-      for (int q = g.z_begin; q < g.z_end; ++q) {
-        const int slot = q % R->slots;
-        {
-          std::unique_lock<std::mutex> lk(drain.m);   // the slot's previous plane has reached the caller's array
-          drain.cv.wait(lk, [&] { return drain.drained > q - R->slots; });
-          if (drain.failed) return fail(TF_ERR_CUDA, "host pipeline: a download did not complete");
-        }
-        TF_CUDA(cudaMemcpyAsync(R->out + (size_t)slot * plane_bytes, d_out + plane * q, plane_bytes, cudaMemcpyDeviceToHost, p.s_d2h));
-        TF_CUDA(cudaEventRecord(R->out_landed[slot], p.s_d2h));
-        { std::lock_guard<std::mutex> lk(drain.m); drain.issued = q + 1; }
-        drain.cv.notify_all();
-      }
-    } else {
-      TF_CUDA(cudaMemcpyAsync(h_out + plane * g.z_begin, d_out + plane * g.z_begin, plane_bytes * (size_t)(g.z_end - g.z_begin),
-                              cudaMemcpyDeviceToHost, p.s_d2h));
-    }
+    TF_CUDA(p.host_pipe->download(h_out + plane * g.z_begin, d_out + plane * g.z_begin, plane_bytes * (size_t)(g.z_end - g.z_begin), p.s_d2h));
   }
   p.launches = launches;
-  if (stage_out) {
-    std::unique_lock<std::mutex> lk(drain.m);
-    drain.cv.wait(lk, [&] { return drain.drained >= M.nz; });
-    if (drain.failed) return fail(TF_ERR_CUDA, "host pipeline: a download did not complete");
-  }
+  TF_CUDA(p.host_pipe->finish());
   TF_CUDA(cudaStreamSynchronize(p.s_d2h));
   TF_CUDA(cudaStreamSynchronize(p.s_run));
   return TF_OK;

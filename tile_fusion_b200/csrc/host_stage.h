@@ -112,4 +112,111 @@ inline bool is_pageable(const void *p) {
   return a.type == cudaMemoryTypeUnregistered;
 }
 
+// One call's copies.  upload() / download() are cudaMemcpyAsync on the given stream for pinned arrays; for pageable
+// ones they go piece by piece through the rings: the calling thread fills upload slots (and waits for the copy engine
+// before it reuses one), a second thread empties download slots into the caller's array as they land.
+class HostPipe {
+ public:
+  explicit HostPipe(int threads) : rings_(threads, threads) {}
+  ~HostPipe() { stop_drainer(); }
+
+  cudaError_t begin(int device, bool stage_in, bool stage_out, size_t piece_bytes, int slots) {
+    stop_drainer();
+    stage_in_ = stage_in; stage_out_ = stage_out;
+    n_up_ = 0; n_down_ = 0; drained_ = 0; failed_ = false; stop_ = false;
+    jobs_.clear();
+    if (!stage_in && !stage_out) return cudaSuccess;
+    cudaError_t e = rings_.reserve(piece_bytes, slots);
+    if (e != cudaSuccess) return e;
+    if (stage_out) drainer_ = std::thread([this, device] { drain(device); });
+    return cudaSuccess;
+  }
+
+  cudaError_t upload(void *d_dst, const void *h_src, size_t bytes, cudaStream_t s) {
+    if (!stage_in_) return cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, s);
+    const size_t piece = rings_.piece_bytes;
+    for (size_t off = 0; off < bytes; off += piece, ++n_up_) {
+      const size_t n = std::min(piece, bytes - off);
+      const int slot = (int)(n_up_ % rings_.slots);
+      cudaError_t e = n_up_ >= (unsigned long long)rings_.slots ? cudaEventSynchronize(rings_.in_sent[slot]) : cudaSuccess;
+      if (e != cudaSuccess) return e;
+      char *buf = rings_.in + (size_t)slot * piece;
+      rings_.crew_in.copy(buf, (const char *)h_src + off, n);
+      e = cudaMemcpyAsync((char *)d_dst + off, buf, n, cudaMemcpyHostToDevice, s);
+      if (e == cudaSuccess) e = cudaEventRecord(rings_.in_sent[slot], s);
+      if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+  }
+
+  cudaError_t download(void *h_dst, const void *d_src, size_t bytes, cudaStream_t s) {
+    if (!stage_out_) return cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, s);
+    const size_t piece = rings_.piece_bytes;
+    for (size_t off = 0; off < bytes; off += piece, ++n_down_) {
+      const size_t n = std::min(piece, bytes - off);
+      const int slot = (int)(n_down_ % rings_.slots);
+      {
+        std::unique_lock<std::mutex> g(m_);   // the slot's previous piece has reached the caller's array
+        cv_.wait(g, [&] { return failed_ || drained_ + (unsigned long long)rings_.slots > n_down_; });
+        if (failed_) return cudaErrorUnknown;
+      }
+      cudaError_t e = cudaMemcpyAsync(rings_.out + (size_t)slot * piece, (const char *)d_src + off, n, cudaMemcpyDeviceToHost, s);
+      if (e == cudaSuccess) e = cudaEventRecord(rings_.out_landed[slot], s);
+      if (e != cudaSuccess) return e;
+      { std::lock_guard<std::mutex> g(m_); jobs_.push_back(Job{(char *)h_dst + off, n, slot}); }
+      cv_.notify_all();
+    }
+    return cudaSuccess;
+  }
+
+  // every download has reached the caller's array
+  cudaError_t finish() {
+    if (!stage_out_) return cudaSuccess;
+    {
+      std::unique_lock<std::mutex> g(m_);
+      cv_.wait(g, [&] { return failed_ || drained_ == n_down_; });
+    }
+    stop_drainer();
+    return failed_ ? cudaErrorUnknown : cudaSuccess;
+  }
+
+ private:
+  struct Job { char *dst; size_t bytes; int slot; };
+  void drain(int device) {
+    cudaSetDevice(device);
+    for (size_t next = 0;; ++next) {
+      Job j;
+      {
+        std::unique_lock<std::mutex> g(m_);
+        cv_.wait(g, [&] { return stop_ || jobs_.size() > next; });
+        if (jobs_.size() <= next) return;
+        j = jobs_[next];
+      }
+      if (cudaEventSynchronize(rings_.out_landed[j.slot]) != cudaSuccess) {
+        std::lock_guard<std::mutex> g(m_);
+        failed_ = true;
+        cv_.notify_all();
+        return;
+      }
+      rings_.crew_out.copy(j.dst, rings_.out + (size_t)j.slot * rings_.piece_bytes, j.bytes);
+      { std::lock_guard<std::mutex> g(m_); ++drained_; }
+      cv_.notify_all();
+    }
+  }
+  void stop_drainer() {
+    { std::lock_guard<std::mutex> g(m_); stop_ = true; }
+    cv_.notify_all();
+    if (drainer_.joinable()) drainer_.join();
+  }
+
+  StageRings rings_;
+  bool stage_in_ = false, stage_out_ = false;
+  unsigned long long n_up_ = 0, n_down_ = 0, drained_ = 0;
+  std::mutex m_;
+  std::condition_variable cv_;
+  std::vector<Job> jobs_;
+  bool stop_ = false, failed_ = false;
+  std::thread drainer_;
+};
+
 }  // namespace tf
