@@ -78,10 +78,9 @@ class ClockSampler:
 
     def _loop(self):
         try:
-            import pynvml as nv
-            nv.nvmlInit()
-            h = nv.nvmlDeviceGetHandleByIndex(self.index)
-            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            nv, h = self._nv, self._h
+            if nv is None:
+                return
             names = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
             while not self._stop.is_set():
                 self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
@@ -97,6 +96,14 @@ class ClockSampler:
             self.reasons.add(f"unavailable:{type(e).__name__}")
 
     def __enter__(self):
+        try:  # NVML is brought up here, not in the thread: its start-up takes longer than a short timed region
+            import pynvml as nv
+            nv.nvmlInit()
+            self._nv, self._h = nv, nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self._h, nv.NVML_CLOCK_SM)
+        except Exception as e:
+            self._nv = self._h = None
+            self.reasons.add(f"unavailable:{type(e).__name__}")
         self._thr = threading.Thread(target=self._loop, daemon=True)
         self._thr.start()
         return self
