@@ -133,6 +133,9 @@ typedef struct {
                              (every nonzero names the row's own grid point or one of its six neighbours):
                              0 = run the plane-marching kernel, which keeps the intermediate in shared memory,
                              <0 = never (general CSR path)                                               */
+  int exchange;           /* tf_multi_plan only: 0 = halo rows are written by the copy engines straight into the
+                             neighbours' memory (CUDA IPC) where every rank is a process of its own on one host,
+                             else ncclSend / ncclRecv; <0 = always ncclSend / ncclRecv (every rank must say the same) */
 } tf_plan_opts;
 
 typedef struct tf_plan tf_plan;

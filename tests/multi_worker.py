@@ -64,6 +64,19 @@ def main():
         nat.status()
         want = (A64 @ (A64 @ c.astype(np.float64)))[r0:r1]
         common.assert_close(d2.cpu().numpy(), want, f"rank {rank} native SpMM-SpMM {dims}")
+        # a traced step: every phase is recorded and ends inside the step
+        nat.trace(True)
+        nat.step(c_ext, None, d2)
+        tr = nat.trace(False)
+        assert tr is not None and all(0 <= tr[k] <= tr["step_done"] + 0.02 for k in tr), tr   # (two streams: 0.02 ms of slack)
+        common.assert_close(d2.cpu().numpy(), want, f"rank {rank} native SpMM-SpMM {dims}, traced step")
+        nat.close()
+        # the same with the halo rows sent through ncclSend / ncclRecv instead of the copy engines: same bits
+        nat = distributed.NativeRankChain("spmm_spmm", rank, world, r0, r1, a_rows, n, dist=dist, device=dev, exchange=-1)
+        d3 = torch.full((r1 - r0, n), float("nan"), device=dev)
+        nat.step(c_ext, None, d3)
+        nat.status()
+        assert torch.equal(d3, d2), "the two exchange paths differ"
         nat.close()
         nat = distributed.NativeRankChain("gemm_spmm", rank, world, r0, r1, a_rows, n, k=k, dist=dist, device=dev)
         d2.fill_(float("nan"))

@@ -34,7 +34,7 @@ class PlanOpts(C.Structure):
                 ("slack_blocks", C.c_int), ("ctas_per_sm", C.c_int), ("halo_rows", C.c_int),
                 ("n_boundary", C.c_int), ("boundary_rows", C.c_void_p), ("tile_slots", C.c_int),
                 ("tile_max_bz", C.c_int), ("tile_double_buffer", C.c_int), ("tensor_cores", C.c_int),
-                ("tile_pipeline", C.c_int), ("lattice_march", C.c_int)]
+                ("tile_pipeline", C.c_int), ("lattice_march", C.c_int), ("exchange", C.c_int)]
 
 
 EXPORTS = [

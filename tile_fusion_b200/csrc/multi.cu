@@ -252,8 +252,9 @@ int gather_records(tf_multi &M, const T &mine, std::vector<T> &all) {
 }
 
 // Collective.  Maps the neighbours' halo rows into this process where that is possible; the direct exchange is
-// used only if every rank could map all it needs (TF_EXCHANGE=nccl in the environment keeps ncclSend / ncclRecv).
-int setup_direct_exchange(tf_multi &M, const std::vector<long long> &bounds, const std::vector<std::vector<long long>> &halos) {
+// used only if every rank could map all it needs (and none asked for ncclSend / ncclRecv: allow_direct).
+int setup_direct_exchange(tf_multi &M, const std::vector<long long> &bounds, const std::vector<std::vector<long long>> &halos,
+                          bool allow_direct) {
   const int world = M.c->world, rank = M.c->rank;
   if (world < 2) return TF_OK;
   ExchangeCard me;
@@ -267,8 +268,7 @@ int setup_direct_exchange(tf_multi &M, const std::vector<long long> &bounds, con
   int cols = 0;
   int rc = tf_plan_intermediate(M.plan, &base, &rows, &cols);
   if (rc != TF_OK) return rc;
-  const char *env = getenv("TF_EXCHANGE");
-  bool can = !(env && std::strcmp(env, "nccl") == 0);
+  bool can = allow_direct;
   if (M.halobuf && base) {
     me.has_halo = 1;
     me.halo_offset = (long long)((const char *)M.halobuf - (const char *)base);
@@ -473,7 +473,7 @@ int tf_multi_plan(tf_comm *c, int chain, long long r0, long long r1, const int *
     TF_CUDA(cudaMemcpy(M->gathers[i].idx, lay.send[i].index.data(), sizeof(long long) * lay.send[i].index.size(), cudaMemcpyHostToDevice));
     TF_CUDA(cudaMalloc(&M->gathers[i].stage, sizeof(float) * lay.send[i].index.size() * n_cols));
   }
-  rc = setup_direct_exchange(*M, bounds, halos);
+  rc = setup_direct_exchange(*M, bounds, halos, !(opts && opts->exchange < 0));
   if (rc != TF_OK) return rc;
   *out = M.release();
   return TF_OK;
@@ -562,8 +562,8 @@ int tf_multi_exec(tf_multi *m, const float *in0, const float *in1, int w_transpo
     // give up -- instead of after it.
     rc = tf_exec_phase(m->plan, 2, in0, in1, w_transposed, relu, D, m->comm_stream);
     if (rc != TF_OK) return rc;
-    TF_CUDA(cudaEventRecord(m->arrived, m->comm_stream));
     if (tr) TF_CUDA(cudaEventRecord(m->tev[3], m->comm_stream));
+    TF_CUDA(cudaEventRecord(m->arrived, m->comm_stream));
     rc = tf_exec_phase(m->plan, 1, in0, in1, w_transposed, relu, D, s);
     if (rc != TF_OK) return rc;
     if (tr) TF_CUDA(cudaEventRecord(m->tev[4], s));

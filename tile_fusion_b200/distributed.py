@@ -131,7 +131,8 @@ class NativeRankChain:
         ap = np.ascontiguousarray(ap, dtype=np.int32)
         ai = np.ascontiguousarray(ai, dtype=np.int64)
         ax = np.ascontiguousarray(ax, dtype=np.float32)
-        o = _lib.PlanOpts(plan_kw.get("mode", 0), plan_kw.get("rows_per_block", 0), 0, -1, 0, 0, 0, None, 0, 0, 0, 0, 0, 0)
+        o = _lib.PlanOpts(plan_kw.get("mode", 0), plan_kw.get("rows_per_block", 0), 0, -1, 0, 0, 0, None, 0, 0, 0, 0, 0, 0,
+                          plan_kw.get("exchange", 0))
         self._h = C.c_void_p()
         _lib.check(L.tf_multi_plan(self._comm, 0 if chain == "spmm_spmm" else 1, int(r0), int(r1), ap.ctypes.data,
                                    ai.ctypes.data, ax.ctypes.data, int(k), int(n_cols), C.byref(o), C.byref(self._h)))
