@@ -150,6 +150,9 @@ struct tf_plan {
     std::vector<float> dict_f, dict_a;   // host copies: the dictionaries travel as kernel parameters
     DevBuf<int4> items;
     int first_idle_sm = INT_MAX;
+    int n_boundary = 0;              // rows of the neighbours' halo that this rank produces (phase 0)
+    DevBuf<int> b_ap, b_ai;
+    DevBuf<float> b_ax;
     DevBuf<tfk::MarchState> st;   // [0]: tickets of phase 1 (or of the whole grid), [1]: of phase 2 -- the two may run side by side
     std::vector<tf::MarchItem> host_items;
     // host-pointer path (single GPU): the grid again, cut into slabs of planes that run one launch each while the
@@ -308,7 +311,7 @@ static_assert(tf::kMarchMaxClasses == tfk::kMarchMaxClassesDev, "host and device
 // Plane-marching executor: taken when both operators of an SpMM-SpMM chain are star stencils on the same
 // grid (lattice.cpp).  The general plan is built as well and serves calls whose operands are not 16-byte
 // aligned.
-int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int halo_rows, int sm_count) {
+int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int halo_rows, int sm_count, const std::vector<int> &boundary_rows) {
   tf::LatticeOp lf, la;
   int rc = tf::analyse_lattice_operator(F.m, F.n, F.ap, F.ai, F.ax, 0, lf);
   if (rc != TF_OK || !lf.ok) return rc;
@@ -367,6 +370,20 @@ int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int halo_rows, int
   if (rc == TF_OK && !M.same) rc = M.pcls_a.upload(la.patch_cls);
   M.dict_a = M.same ? lf.dict : la.dict;
   if (rc == TF_OK) rc = M.st.alloc(2);
+  if (rc == TF_OK && !boundary_rows.empty()) {
+    // phase 0 of such a plan: the boundary rows of the first operator as a CSR of their own, in send-buffer order
+    std::vector<int> bp(1, 0), bi;
+    std::vector<float> bx;
+    for (int r : boundary_rows) {
+      bi.insert(bi.end(), F.ai + F.ap[r], F.ai + F.ap[r + 1]);
+      bx.insert(bx.end(), F.ax + F.ap[r], F.ax + F.ap[r + 1]);
+      bp.push_back((int)bi.size());
+    }
+    M.n_boundary = (int)boundary_rows.size();
+    rc = M.b_ap.upload(bp);
+    if (rc == TF_OK) rc = M.b_ai.upload(bi);
+    if (rc == TF_OK) rc = M.b_ax.upload(bx);
+  }
   if (rc != TF_OK) return rc;
   TF_CUDA(cudaMemset(M.st.p, 0, 2 * sizeof(tfk::MarchState)));
   M.on = true;
@@ -581,7 +598,7 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
     if (rc != TF_OK) return rc;
   }
   if (chain == 0 && F && o.mode == TF_MODE_STREAM && o.lattice_march >= 0 && o.ring_bytes <= 0 && n_cols % 4 == 0) {
-    rc = build_march(*p, *F, *A, o.halo_rows, sm_count);
+    rc = build_march(*p, *F, *A, o.halo_rows, sm_count, pp.boundary_rows);
     if (rc != TF_OK) return rc;
   }
   *out = p.release();
@@ -1014,8 +1031,19 @@ int tf_exec_phase(tf_plan *p, int phase, const float *in0, const float *in1, int
   if (phase > 0 && !D) return fail(TF_ERR_ARG, "tf_exec_phase: null output");
   int rc = set_device(*p);
   if (rc != TF_OK) return rc;
-  // plane-marching plans: phase 0 (boundary rows of T for the neighbours) runs on the general executor, phases
-  // 1 and 2 on the marching kernel, the second with the received planes of T
+  // plane-marching plans: phase 0 (boundary rows of T for the neighbours: two planes at most) is a plain CSR product
+  // of those rows into the send buffer -- a fraction of the time the general executor's launch takes for so little
+  // work --, phases 1 and 2 run on the marching kernel, the second with the received planes of T
+  if (phase == 0 && p->chain == 0 && p->march.on && p->march.n_boundary > 0 && aligned(in0, 16)) {
+    const tf_plan::March &M = p->march;
+    int vec, ch;
+    tfk::choose_shape(p->n_cols, aligned(in0, 16) && aligned(p->sendbuf.p, 16), &vec, &ch);
+    const int grid = std::max(1, std::min((M.n_boundary + tfk::kWarps - 1) / tfk::kWarps, 148 * 8));
+    TF_CUDA(tfk::launch_spmm(vec, ch, grid, M.b_ap.p, M.b_ai.p, M.b_ax.p, M.n_boundary, in0, p->n_cols, p->sendbuf.p,
+                             (cudaStream_t)stream));
+    p->launches = 1;
+    return TF_OK;
+  }
   if (phase > 0 && p->chain == 0 && march_usable(*p, in0, D))
     return phase == 1 ? run_march(*p, in0, D, 0, p->march.n_phase1, false, (cudaStream_t)stream)
                       : run_march(*p, in0, D, p->march.n_phase1, p->march.n_items, true, (cudaStream_t)stream);
