@@ -144,20 +144,16 @@ __device__ __forceinline__ void patch_start(float4 (&acc)[4], float (&czp)[4],
   czp[3] = row_start(acc[3], dict, word >> 24, prev[3], own[1], own[2], own[3], nb[3], nb[7]);
 }
 
-// Class words of one patch column: the word of plane z, or the all-zero class outside the grid.
+// Class words of one patch column: the word of plane z, or the all-zero class outside the grid.  Only the
+// column's pointer is per thread; the plane pitch, the plane count and the all-zero word are the same for every
+// column and come from the kernel's parameters.
 struct ClassColumn {
-  const unsigned *p;  // word of plane 0 (valid only when inside)
-  unsigned zero_word;
-  int plane_words, nz;
-  bool inside;
-  __device__ __forceinline__ void init(const unsigned *pcls, int x, int y, int nx, int ny, int nz_, int pnx, int pny,
-                                       unsigned zero) {
-    inside = x >= 0 && x < nx && y >= 0 && y < ny;
-    p = pcls + (inside ? (y >> 1) * pnx + (x >> 1) : 0);
-    plane_words = pnx * pny; nz = nz_; zero_word = zero;
+  const unsigned *p;  // word of plane 0; null outside the grid
+  __device__ __forceinline__ void init(const unsigned *pcls, int x, int y, int nx, int ny, int pnx) {
+    p = (x >= 0 && x < nx && y >= 0 && y < ny) ? pcls + ((y >> 1) * pnx + (x >> 1)) : nullptr;
   }
-  __device__ __forceinline__ unsigned at(int z) const {
-    return (inside && (unsigned)z < (unsigned)nz) ? __ldg(p + (size_t)z * plane_words) : zero_word;
+  __device__ __forceinline__ unsigned at(int z, int nz, int plane_words, unsigned zero_word) const {
+    return (p != nullptr && (unsigned)z < (unsigned)nz) ? __ldg(p + (size_t)z * plane_words) : zero_word;
   }
 };
 
@@ -249,7 +245,7 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     roR[r] = yb + xoff<PC>(rx[r] - x0 + 3);
     roT[r] = (ry[r] - y0 + 1) * (PT * 64) + xoff<PT>(rx[r] - x0 + 1) + c4 * 16;
     rsh[r] = 8u * (2u * (ry[r] & 1) + (rx[r] & 1));
-    cr_col[r].init(P.pcls_f, rx[r], ry[r], P.nx, P.ny, P.nz, P.pnx, P.pny, 0x01010101u * (unsigned)P.ncls_f);
+    cr_col[r].init(P.pcls_f, rx[r], ry[r], P.nx, P.ny, P.pnx);
   }
   const int col = c0col + 4 * c4;
   // rows of the patch that exist and whose columns exist: bit j
@@ -262,8 +258,10 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
   float *dptr = P.out + ((size_t)y * P.nx + x) * P.n_cols + col + (long long)(kfirst - 2) * (long long)plane_floats;
   const size_t drow = (size_t)P.nx * P.n_cols;
   ClassColumn cf_col, ca_col;
-  cf_col.init(P.pcls_f, x, y, P.nx, P.ny, P.nz, P.pnx, P.pny, 0x01010101u * (unsigned)P.ncls_f);
-  ca_col.init(P.pcls_a, x, y, P.nx, P.ny, P.nz, P.pnx, P.pny, 0x01010101u * (unsigned)P.ncls_a);
+  cf_col.init(P.pcls_f, x, y, P.nx, P.ny, P.pnx);
+  ca_col.init(P.pcls_a, x, y, P.nx, P.ny, P.pnx);
+  const int plane_words = P.pnx * P.pny;
+  const unsigned zero_f = 0x01010101u * (unsigned)P.ncls_f, zero_a = 0x01010101u * (unsigned)P.ncls_a;
   // The rows of T and D under way and the z+ coefficients they still need.  The own rows of C(k-1) / C(k), of
   // T(k-2) / T(k-1), the ring's own rows and the class words live in two sets of registers: set A is what the step
   // before left, set B what this step writes.
@@ -278,10 +276,10 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
 #pragma unroll
   for (int r = 0; r < kRing; ++r) {
     rA[r] = zero4(); accR[r] = zero4(); czpR[r] = 0.f;
-    wrA[r] = ring ? cr_col[r].at(kfirst) : 0u;
+    wrA[r] = ring ? cr_col[r].at(kfirst, P.nz, plane_words, zero_f) : 0u;
   }
-  unsigned wfA = cf_col.at(kfirst), wfB;
-  unsigned waA = ca_col.zero_word, waB;  // classes of the second operator's rows of plane k - 1
+  unsigned wfA = cf_col.at(kfirst, P.nz, plane_words, zero_f), wfB;
+  unsigned waA = zero_a, waB;  // classes of the second operator's rows of plane k - 1
 
   // One step: plane C(k) arrives.  (cprev, tprev, rprev, wf, wa, wr) were written by the step before;
   // (own, tcur, rown, wf_next, wa_next, wr_next) are written here.
@@ -325,10 +323,10 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     if (lane == 0) mbar_arrive(S.tbar);
     // The class words of the next step are fetched only now: the arrive above is a release, which waits
     // for every load the thread has in flight, and a load from global memory can take a microsecond.
-    wf_next = cf_col.at(k + 1);
-    wa_next = ca_col.at(k);
+    wf_next = cf_col.at(k + 1, P.nz, plane_words, zero_f);
+    wa_next = ca_col.at(k, P.nz, plane_words, zero_a);
 #pragma unroll
-    for (int r = 0; r < kRing; ++r) wr_next[r] = ring ? cr_col[r].at(k + 1) : 0u;
+    for (int r = 0; r < kRing; ++r) wr_next[r] = ring ? cr_col[r].at(k + 1, P.nz, plane_words, zero_f) : 0u;
     // D(k-2) is complete with its z+ product
     if (k - 2 >= zs && k - 2 < ze) {
 #pragma unroll
