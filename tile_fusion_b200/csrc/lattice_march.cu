@@ -104,18 +104,25 @@ __device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.
 // In-plane neighbours of a 2 x 2 patch in a rectangle of pitch P.  xo[a + 1] = byte offset of the patch's
 // column a (-1 .. 2) inside a y-row, lane's 16 bytes included; yo = byte offset of the patch's first y-row.
 // nb: [0, 2) left column, [2, 4) right column, [4, 6) row below, [6, 8) row above.
-// `col[a + 1]` = address of the patch's first y-row at the patch's column a (-1 .. 2), lane's 16 bytes included.
-template <int P>
-__device__ __forceinline__ void load_nb(const unsigned (&col)[4], float4 (&nb)[8]) {
-  nb[0] = lds4i<0>(col[0]);          nb[1] = lds4i<P * 64>(col[0]);
-  nb[2] = lds4i<0>(col[3]);          nb[3] = lds4i<P * 64>(col[3]);
-  nb[4] = lds4i<-P * 64>(col[1]);    nb[5] = lds4i<-P * 64>(col[2]);
-  nb[6] = lds4i<2 * P * 64>(col[1]); nb[7] = lds4i<2 * P * 64>(col[2]);
+// A patch starts at an even x of its tile (x - x0 = 2 * pi), so in a rectangle of pitch P whose column 0 holds
+// x0 - R0 the patch's columns a = -1 .. 2 sit at fixed byte distances co<P, R0>(a) from `base` = the address of
+// (column of x0 - R0 + 2 * pi ... i.e. pi * 64 bytes into the row, lane's 16 bytes included) of the patch's first
+// y-row: one register addresses all twelve loads of a patch.
+template <int P, int R0>
+__host__ __device__ constexpr int co(int a) { return ((R0 + a) & 1) * (P / 2 * 64) + ((R0 + a) >> 1) * 64; }
+
+// nb: [0, 2) left column, [2, 4) right column, [4, 6) row below, [6, 8) row above.
+template <int P, int R0>
+__device__ __forceinline__ void load_nb(unsigned base, float4 (&nb)[8]) {
+  nb[0] = lds4i<co<P, R0>(-1)>(base);             nb[1] = lds4i<co<P, R0>(-1) + P * 64>(base);
+  nb[2] = lds4i<co<P, R0>(2)>(base);              nb[3] = lds4i<co<P, R0>(2) + P * 64>(base);
+  nb[4] = lds4i<co<P, R0>(0) - P * 64>(base);     nb[5] = lds4i<co<P, R0>(1) - P * 64>(base);
+  nb[6] = lds4i<co<P, R0>(0) + 2 * P * 64>(base); nb[7] = lds4i<co<P, R0>(1) + 2 * P * 64>(base);
 }
-template <int P>
-__device__ __forceinline__ void load_own(const unsigned (&col)[4], float4 (&own)[4]) {
-  own[0] = lds4i<0>(col[1]);      own[1] = lds4i<0>(col[2]);
-  own[2] = lds4i<P * 64>(col[1]); own[3] = lds4i<P * 64>(col[2]);
+template <int P, int R0>
+__device__ __forceinline__ void load_own(unsigned base, float4 (&own)[4]) {
+  own[0] = lds4i<co<P, R0>(0)>(base);          own[1] = lds4i<co<P, R0>(1)>(base);
+  own[2] = lds4i<co<P, R0>(0) + P * 64>(base); own[3] = lds4i<co<P, R0>(1) + P * 64>(base);
 }
 
 // Starts one row: acc = its first six products in sorted-column order -- z- (from `zm`, the same grid point one
@@ -226,27 +233,24 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
                                          const volatile int *next, int &prefetched) {
   const int tid = threadIdx.x, lane = tid & 31, c4 = lane & 3;
   const int kfirst = zs - lead_in(zs, P), steps = ze - kfirst + 2;
-  // byte offsets of the patch's first y-row at its columns -1 .. 2, in the C and in the T rectangle
-  int coC[4], coT[4];
-#pragma unroll
-  for (int a = -1; a <= 2; ++a) {
-    coC[a + 1] = (y - y0 + 2) * (PC * 64) + xoff<PC>(x - x0 + 2 + a) + c4 * 16;
-    coT[a + 1] = (y - y0 + 1) * (PT * 64) + xoff<PT>(x - x0 + 1 + a) + c4 * 16;
-  }
-  // ring rows: offsets of the row and of its left / right neighbour in the C rectangle, of the row in the T one
-  int roC[kRing], roL[kRing], roR[kRing], roT[kRing];
-  unsigned rsh[kRing];  // bit position of the row's class in its patch's class word
-  ClassColumn cr_col[kRing];
-#pragma unroll
-  for (int r = 0; r < kRing; ++r) {
-    const int yb = (ry[r] - y0 + 2) * (PC * 64) + c4 * 16;
-    roC[r] = yb + xoff<PC>(rx[r] - x0 + 2);
-    roL[r] = yb + xoff<PC>(rx[r] - x0 + 1);
-    roR[r] = yb + xoff<PC>(rx[r] - x0 + 3);
-    roT[r] = (ry[r] - y0 + 1) * (PT * 64) + xoff<PT>(rx[r] - x0 + 1) + c4 * 16;
-    rsh[r] = 8u * (2u * (ry[r] & 1) + (rx[r] & 1));
-    cr_col[r].init(P.pcls_f, rx[r], ry[r], P.nx, P.ny, P.pnx);
-  }
+  // byte offset of the patch's first y-row (at pi * 64 bytes into it, lane's 16 bytes included) in the C rectangle
+  // (two points of rim: R0 = 2) and in the T rectangle (one point: R0 = 1)
+  const int pi64 = (x - x0) * 32 + c4 * 16;
+  const int boC = (y - y0 + 2) * (PC * 64) + pi64, boT = (y - y0 + 1) * (PT * 64) + pi64;
+  // The group's two ring rows are neighbours (in x below / above the tile, in y beside it) and lie in one 2 x 2 class
+  // patch.  Offsets of the first row, of its left neighbour and of the right neighbour (of the second row when
+  // the pair lies along x) in the C rectangle, of the first row in the T rectangle; the second row's follow by
+  // constants.
+  const int ybr = (ry[0] - y0 + 2) * (PC * 64) + c4 * 16;
+  const int rC = ybr + xoff<PC>(rx[0] - x0 + 2), rL = ybr + xoff<PC>(rx[0] - x0 + 1);
+  const int rR = ybr + xoff<PC>(rx[0] - x0 + (pair_x ? 4 : 3));
+  const int rT = (ry[0] - y0 + 1) * (PT * 64) + xoff<PT>(rx[0] - x0 + 1) + c4 * 16;
+  const unsigned rsh0 = 8u * (2u * (ry[0] & 1) + (rx[0] & 1));  // bit position of the first row's class in the class word
+  ClassColumn cr_col;
+  cr_col.init(P.pcls_f, rx[0], ry[0], P.nx, P.ny, P.pnx);
+  // second row: distances in the C rectangle, in the T rectangle and in the class word
+  constexpr int kX1C = PC / 2 * 64, kY1C = PC * 64;       // x + 1 from an even column / y + 1
+  constexpr int kX1T = 64 - PT / 2 * 64, kY1T = PT * 64;  // x + 1 from an odd column / y + 1
   const int col = c0col + 4 * c4;
   // rows of the patch that exist and whose columns exist: bit j
   unsigned live = 0;
@@ -272,12 +276,9 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     cA[j] = zero4(); tA[j] = zero4(); accT[j] = zero4(); accD[j] = zero4();
     czpT[j] = 0.f; czpD[j] = 0.f;
   }
-  unsigned wrA[kRing], wrB[kRing];
 #pragma unroll
-  for (int r = 0; r < kRing; ++r) {
-    rA[r] = zero4(); accR[r] = zero4(); czpR[r] = 0.f;
-    wrA[r] = ring ? cr_col[r].at(kfirst, P.nz, plane_words, zero_f) : 0u;
-  }
+  for (int r = 0; r < kRing; ++r) { rA[r] = zero4(); accR[r] = zero4(); czpR[r] = 0.f; }
+  unsigned wrA = ring ? cr_col.at(kfirst, P.nz, plane_words, zero_f) : 0u, wrB;
   unsigned wfA = cf_col.at(kfirst, P.nz, plane_words, zero_f), wfB;
   unsigned waA = zero_a, waB;  // classes of the second operator's rows of plane k - 1
 
@@ -285,18 +286,18 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
   // (own, tcur, rown, wf_next, wa_next, wr_next) are written here.
   auto one_step = [&](int step, float4 (&cprev)[4], float4 (&own)[4], float4 (&tprev)[4], float4 (&tcur)[4],
                       float4 (&rprev)[kRing], float4 (&rown)[kRing], unsigned wf, unsigned &wf_next, unsigned wa,
-                      unsigned &wa_next, unsigned (&wr)[kRing], unsigned (&wr_next)[kRing]) -> bool {
+                      unsigned &wa_next, unsigned wr, unsigned &wr_next) -> bool {
     const int k = kfirst + step;
     const unsigned stage = cs.n_use % kMarchStages;
     if (!wait_or_abort(S.full + 8 * stage, (cs.n_use / kMarchStages) & 1u, P.wait_limit, S.abort)) return false;
     const unsigned cb = S.cbuf + stage * kMarchCBytes;
     float4 nb[8];
-    const unsigned colC[4] = {cb + coC[0], cb + coC[1], cb + coC[2], cb + coC[3]};
-    load_own<PC>(colC, own);
-    load_nb<PC>(colC, nb);
+    const unsigned baseC = cb + boC;
+    load_own<PC, 2>(baseC, own);
+    load_nb<PC, 2>(baseC, nb);
     if (ring) {
-#pragma unroll
-      for (int r = 0; r < kRing; ++r) rown[r] = lds4(cb, roC[r]);
+      rown[0] = lds4(cb, rC);
+      rown[1] = pair_x ? lds4i<kX1C>(cb + rC) : lds4i<kY1C>(cb + rC);
     }
     // T(k-1) is complete with its z+ product
     const unsigned tb = S.tbuf + ((k - 1) & 1) * kMarchTBytes;
@@ -306,18 +307,16 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
       tcur[j] = fma4(czpT[j], own[j], accT[j]);
       if (halo) tcur[j] = halo_row(halo, x + (j & 1), y + (j >> 1), col, P);
     }
-    const unsigned colT[4] = {tb + coT[0], tb + coT[1], tb + coT[2], tb + coT[3]};
+    const unsigned baseT = tb + boT;
     // (the buffer of T(k-1) was last read in step k-2; this thread has waited for every warp's arrival of
     // step k-1, which each warp gives after its reads of step k-2)
-    sts4i<0>(colT[1], tcur[0]);       sts4i<0>(colT[2], tcur[1]);
-    sts4i<PT * 64>(colT[1], tcur[2]); sts4i<PT * 64>(colT[2], tcur[3]);
+    sts4i<co<PT, 1>(0)>(baseT, tcur[0]);           sts4i<co<PT, 1>(1)>(baseT, tcur[1]);
+    sts4i<co<PT, 1>(0) + PT * 64>(baseT, tcur[2]); sts4i<co<PT, 1>(1) + PT * 64>(baseT, tcur[3]);
     if (ring) {
-#pragma unroll
-      for (int r = 0; r < kRing; ++r) {
-        float4 t = fma4(czpR[r], rown[r], accR[r]);
-        if (halo) t = halo_row(halo, rx[r], ry[r], col, P);
-        sts4(tb, roT[r], t);
-      }
+      float4 t0 = fma4(czpR[0], rown[0], accR[0]), t1 = fma4(czpR[1], rown[1], accR[1]);
+      if (halo) { t0 = halo_row(halo, rx[0], ry[0], col, P); t1 = halo_row(halo, rx[1], ry[1], col, P); }
+      sts4(tb, rT, t0);
+      if (pair_x) sts4i<kX1T>(tb + rT, t1); else sts4i<kY1T>(tb + rT, t1);
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(S.tbar);
@@ -325,8 +324,7 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     // for every load the thread has in flight, and a load from global memory can take a microsecond.
     wf_next = cf_col.at(k + 1, P.nz, plane_words, zero_f);
     wa_next = ca_col.at(k, P.nz, plane_words, zero_a);
-#pragma unroll
-    for (int r = 0; r < kRing; ++r) wr_next[r] = ring ? cr_col[r].at(k + 1, P.nz, plane_words, zero_f) : 0u;
+    wr_next = ring ? cr_col.at(k + 1, P.nz, plane_words, zero_f) : 0u;
     // D(k-2) is complete with its z+ product
     if (k - 2 >= zs && k - 2 < ze) {
 #pragma unroll
@@ -341,22 +339,21 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
       if (ring) {
         // (the ring rows' neighbours are read only now, when the patch's are no longer needed; the stage is
         // refilled one step later, see below)
+        const unsigned cls0 = (wr >> rsh0) & 255u;
         if (pair_x) {
           // the group's two ring rows are neighbours in x: each is the other's x- / x+ row
-          const float4 ym0 = lds4i<-PC * 64>(cb + roC[0]), xm0 = lds4(cb, roL[0]), yp0 = lds4i<PC * 64>(cb + roC[0]);
-          czpR[0] = row_start(accR[0], P.dict_f, (wr[0] >> rsh[0]) & 255u, rprev[0], ym0, xm0, rown[0], rown[kRing - 1], yp0);
-          const float4 ym1 = lds4i<-PC * 64>(cb + roC[kRing - 1]), xp1 = lds4(cb, roR[kRing - 1]);
-          const float4 yp1 = lds4i<PC * 64>(cb + roC[kRing - 1]);
-          czpR[kRing - 1] = row_start(accR[kRing - 1], P.dict_f, (wr[kRing - 1] >> rsh[kRing - 1]) & 255u, rprev[kRing - 1], ym1,
-                                      rown[0], rown[kRing - 1], xp1, yp1);
+          const unsigned cls1 = (wr >> (rsh0 + 8u)) & 255u;
+          const float4 ym0 = lds4i<-PC * 64>(cb + rC), xm0 = lds4(cb, rL), yp0 = lds4i<PC * 64>(cb + rC);
+          czpR[0] = row_start(accR[0], P.dict_f, cls0, rprev[0], ym0, xm0, rown[0], rown[1], yp0);
+          const float4 ym1 = lds4i<kX1C - PC * 64>(cb + rC), xp1 = lds4(cb, rR), yp1 = lds4i<kX1C + PC * 64>(cb + rC);
+          czpR[1] = row_start(accR[1], P.dict_f, cls1, rprev[1], ym1, rown[0], rown[1], xp1, yp1);
         } else {
           // ... neighbours in y: each is the other's y- / y+ row
-          const float4 ym0 = lds4i<-PC * 64>(cb + roC[0]), xm0 = lds4(cb, roL[0]), xp0 = lds4(cb, roR[0]);
-          czpR[0] = row_start(accR[0], P.dict_f, (wr[0] >> rsh[0]) & 255u, rprev[0], ym0, xm0, rown[0], xp0, rown[kRing - 1]);
-          const float4 xm1 = lds4(cb, roL[kRing - 1]), xp1 = lds4(cb, roR[kRing - 1]);
-          const float4 yp1 = lds4i<PC * 64>(cb + roC[kRing - 1]);
-          czpR[kRing - 1] = row_start(accR[kRing - 1], P.dict_f, (wr[kRing - 1] >> rsh[kRing - 1]) & 255u, rprev[kRing - 1],
-                                      rown[0], xm1, rown[kRing - 1], xp1, yp1);
+          const unsigned cls1 = (wr >> (rsh0 + 16u)) & 255u;
+          const float4 ym0 = lds4i<-PC * 64>(cb + rC), xm0 = lds4(cb, rL), xp0 = lds4(cb, rR);
+          czpR[0] = row_start(accR[0], P.dict_f, cls0, rprev[0], ym0, xm0, rown[0], xp0, rown[1]);
+          const float4 xm1 = lds4i<kY1C>(cb + rL), xp1 = lds4i<kY1C>(cb + rR), yp1 = lds4i<2 * PC * 64>(cb + rC);
+          czpR[1] = row_start(accR[1], P.dict_f, cls1, rprev[1], rown[0], xm1, rown[1], xp1, yp1);
         }
       }
     }
@@ -386,7 +383,7 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
     // D(k-1): everything but the z+ product, from T(k-2) (registers), T(k-1) (registers and neighbours)
     if (k - 1 >= zs && k - 1 < ze) {
       float4 tn[8];
-      load_nb<PT>(colT, tn);
+      load_nb<PT, 1>(baseT, tn);
       patch_start(accD, czpD, P.dict_a, wa, tprev, tcur, tn);
     }
     ++cs.n_use;
@@ -401,8 +398,8 @@ __device__ __forceinline__ bool run_item(const CUtensorMap *tm_c, const MarchPar
 #pragma unroll
     for (int j = 0; j < 4; ++j) { cA[j] = cB[j]; tA[j] = tB[j]; }
 #pragma unroll
-    for (int r = 0; r < kRing; ++r) { rA[r] = rB[r]; wrA[r] = wrB[r]; }
-    wfA = wfB; waA = waB;
+    for (int r = 0; r < kRing; ++r) rA[r] = rB[r];
+    wfA = wfB; waA = waB; wrA = wrB;
   }
   return true;
 }
