@@ -52,7 +52,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on the full workload, from
 # the ncu capture summarised in profiles/lattice_march_kernel_spmm_spmm_laplacian3d.md
-DRAM_TRAFFIC = {"c2": 1_207_925_000 + 1_040_525_000}
+DRAM_TRAFFIC = {"c2": 1_201_267_000 + 1_042_153_000}
 
 # TileM values (bytes of cache per tile) of the reference's own sweep, fusion/scripts/run_exp.sh mode 7, thinned
 TILE_M_SWEEP = (60_000, 300_000, 1_250_000)
