@@ -708,7 +708,7 @@ def main():
     line = run_lattice_workload(args.workload, args, ctx, headline=True)
     also = []
     if args.workload == "c2" and not args.quick:
-        # the chain BASELINE.json's metric names: GeMM-SpMM, 256^3 over these ranks (strong scaling), 256^2 on one GPU
+        # the reference's headline chain: GeMM-SpMM, 256^3 over these ranks (strong scaling), 256^2 on one GPU
         for extra in (["c5", "c1"] if world == 1 else ["c5"]):
             try:
                 r = run_lattice_workload(extra, args, ctx, headline=False)
