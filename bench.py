@@ -524,9 +524,12 @@ def run_lattice_workload(name, args, ctx, headline):
     achieved = bytes_local / (kernel_ms * 1e-3) / 1e9
     threads = plan.info()["threads"]
     kernel = {128: "lattice_march_kernel", 672: "tile_pipeline_kernel"}.get(threads, "stream_kernel")
+    if chain == "gemm_spmm" and threads == 128:
+        kernel = "tc_gemm_kernel (dense producer) + lattice_march_kernel"
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": None, "peak_source": f"of {peak_kind}", "algorithmic_bytes_per_launch": bytes_local,
-                "kernel": kernel + " (persistent fused executor)", "kernel_ms": kernel_ms,
+                "kernel": kernel + (" (persistent fused executor)" if "+" not in kernel else " (two launches per step)"),
+                "kernel_ms": kernel_ms,
                 "kernel_ms_min": float(np.min(per_step))}
     if world == 1 and args.mode == "stream" and name in DRAM_TRAFFIC and kernel == "lattice_march_kernel" and not args.dims:
         roofline["traffic"] = DRAM_TRAFFIC[name]

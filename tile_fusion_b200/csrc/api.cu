@@ -137,12 +137,14 @@ struct tf_plan {
   int pipe_grid = 0, pipe_rows = 0;
   // tensor-core dense producer
   bool use_tc = false;
+  int sm_count = 0;
   DevBuf<float> w_hi, w_lo;  // split, transposed weight [n_cols][k]
   CUtensorMap tm_whi, tm_wlo;
   int tile_info[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // producer bx,by,bz,tiles ; consumer bx,by,bz,tiles
   // plane-marching executor (both operators are star stencils on one grid)
   struct March {
     bool on = false, same = false;  // same: one operator on both sides (B == A)
+    bool identity_first = false;    // GeMM-SpMM: the first operator is the identity, the operand is the producer's T
     bool halo_lo = false, halo_hi = false;  // a neighbour rank below / above supplies plane -1 / nz of T
     int nx = 0, ny = 0, nz = 0, ncls_f = 0, ncls_a = 0, z_shift = 0, grid = 0, n_items = 0, n_phase1 = 0;
     long long planes_c = 0;
@@ -311,15 +313,33 @@ static_assert(tf::kMarchMaxClasses == tfk::kMarchMaxClassesDev, "host and device
 // Plane-marching executor: taken when both operators of an SpMM-SpMM chain are star stencils on the same
 // grid (lattice.cpp).  The general plan is built as well and serves calls whose operands are not 16-byte
 // aligned.
-int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int halo_rows, int sm_count, const std::vector<int> &boundary_rows) {
+// Fp == null: the first operator is the identity (GeMM-SpMM: the dense producer has written T, and the marching
+// kernel computes D = A * (I * T); the products with the identity's zeros and its one are exact, so D is what the
+// CSR consumer gives).
+int build_march(tf_plan &p, const tf_csr *Fp, const tf_csr &A, int halo_rows, int sm_count, const std::vector<int> &boundary_rows) {
   tf::LatticeOp lf, la;
-  int rc = tf::analyse_lattice_operator(F.m, F.n, F.ap, F.ai, F.ax, 0, lf);
-  if (rc != TF_OK || !lf.ok) return rc;
-  if (&F == &A && halo_rows == 0) la = lf;
+  int rc = TF_OK;
+  if (Fp) {
+    rc = tf::analyse_lattice_operator(Fp->m, Fp->n, Fp->ap, Fp->ai, Fp->ax, 0, lf);
+    if (rc != TF_OK || !lf.ok) return rc;
+  }
+  if (Fp == &A && halo_rows == 0) la = lf;
   else {
     rc = tf::analyse_lattice_operator(A.m, A.n, A.ap, A.ai, A.ax, halo_rows, la);
     if (rc != TF_OK || !la.ok) return rc;
   }
+  if (!Fp) {
+    lf.ok = true; lf.nx = la.nx; lf.ny = la.ny; lf.nz = la.nz; lf.n_classes = 1;
+    lf.dict.assign(16, 0.f);
+    lf.dict[3] = 1.f;                    // class 0: centre coefficient 1; class 1: all zero
+    lf.patch_cls = la.patch_cls;         // same rows exist: zero class where A has none
+    for (uint32_t &w : lf.patch_cls) {
+      uint32_t v = 0;
+      for (int b = 0; b < 4; ++b) v |= (uint32_t)(((w >> (8 * b)) & 255u) == (uint32_t)la.n_classes ? 1u : 0u) << (8 * b);
+      w = v;
+    }
+  }
+  const tf_csr &F = Fp ? *Fp : A;
   if (la.nx != lf.nx || la.ny != lf.ny || la.nz != lf.nz) return TF_OK;
   if (halo_rows == 0 && (la.ghost_lo || la.ghost_hi)) return TF_OK;
   // with a neighbour rank below (above), the first operator must reach one plane of C below (above) the rank's
@@ -366,11 +386,12 @@ int build_march(tf_plan &p, const tf_csr &F, const tf_csr &A, int halo_rows, int
   rc = M.items.upload(raw);
   if (rc == TF_OK) rc = M.pcls_f.upload(lf.patch_cls);
   M.dict_f = lf.dict;
-  M.same = &F == &A && halo_rows == 0;
+  M.same = Fp == &A && halo_rows == 0;
+  M.identity_first = Fp == nullptr;
   if (rc == TF_OK && !M.same) rc = M.pcls_a.upload(la.patch_cls);
   M.dict_a = M.same ? lf.dict : la.dict;
   if (rc == TF_OK) rc = M.st.alloc(2);
-  if (rc == TF_OK && !boundary_rows.empty()) {
+  if (rc == TF_OK && Fp && !boundary_rows.empty()) {
     // phase 0 of such a plan: the boundary rows of the first operator as a CSR of their own, in send-buffer order
     std::vector<int> bp(1, 0), bi;
     std::vector<float> bx;
@@ -598,9 +619,16 @@ int make_chain_plan(int chain, const tf_csr *A, const tf_csr *B, int k_dim, int 
     if (rc != TF_OK) return rc;
   }
   if (chain == 0 && F && o.mode == TF_MODE_STREAM && o.lattice_march >= 0 && o.ring_bytes <= 0 && n_cols % 4 == 0) {
-    rc = build_march(*p, *F, *A, o.halo_rows, sm_count, pp.boundary_rows);
+    rc = build_march(*p, F, *A, o.halo_rows, sm_count, pp.boundary_rows);
     if (rc != TF_OK) return rc;
   }
+  // GeMM-SpMM with a grid operator, the tensor-core producer and the whole intermediate in memory: the consumer is
+  // the marching kernel
+  if (chain == 1 && o.mode == TF_MODE_STREAM && o.lattice_march >= 0 && p->use_tc && p->hp.ring_rows == 0 && n_cols % 4 == 0) {
+    rc = build_march(*p, nullptr, *A, o.halo_rows, sm_count, pp.boundary_rows);
+    if (rc != TF_OK) return rc;
+  }
+  p->sm_count = sm_count;
   *out = p.release();
   return TF_OK;
 }
@@ -1000,6 +1028,29 @@ int tf_exec_spmm_spmm(tf_plan *p, const float *C, float *D, void *stream) {
   return run_chain(*p, P, (cudaStream_t)stream);
 }
 
+// GeMM-SpMM on a grid operator: the dense producer writes all rows of T (one launch of the tensor-core kernel), the
+// marching kernel consumes them (items [item_begin, item_end)).
+int run_gemm_march(tf_plan &p, const float *B, const float *W, int w_transposed, float *D, bool produce, int item_begin,
+                   int item_end, bool with_halo, cudaStream_t s) {
+  long long launches = 0;
+  if (produce) {
+    tfk::Params P = base_params(p);
+    P.in0 = B; P.in1 = W; P.w_transposed = w_transposed;
+    int rc = prepare_tc(p, P, s);
+    if (rc != TF_OK) return rc;
+    TF_CUDA(tfk::tc_launch_gemm(P.tm_a, P.tm_whi, P.tm_wlo, p.m, p.k_dim, p.n_cols, p.inter.p, &p.march.st.p[0].error, p.spin_limit,
+                                p.sm_count, s));
+    launches = 2;   // weight split + producer
+  }
+  int rc = run_march(p, p.inter.p, D, item_begin, item_end, with_halo, s);
+  p.launches += launches;
+  return rc;
+}
+
+bool gemm_march_usable(const tf_plan &p, const float *B, const float *D, int relu) {
+  return p.chain == 1 && p.march.on && p.march.identity_first && !relu && aligned(B, 16) && aligned(D, 16);
+}
+
 int tf_exec_gemm_spmm(tf_plan *p, const float *B, const float *W, int w_transposed, int relu, float *D,
                       void *stream) {
   if (!p || !B || !W || !D) return fail(TF_ERR_ARG, "tf_exec_gemm_spmm: null argument");
@@ -1007,6 +1058,8 @@ int tf_exec_gemm_spmm(tf_plan *p, const float *B, const float *W, int w_transpos
   if (p->halo_rows || p->sendbuf.n) return fail(TF_ERR_ARG, "tf_exec_gemm_spmm: plan has halo rows, drive it with tf_exec_phase");
   int rc = set_device(*p);
   if (rc != TF_OK) return rc;
+  if (gemm_march_usable(*p, B, D, relu))
+    return run_gemm_march(*p, B, W, w_transposed, D, true, 0, p->march.n_items, false, (cudaStream_t)stream);
   tfk::Params P = base_params(*p);
   P.in0 = B; P.in1 = W; P.out = D; P.w_transposed = w_transposed; P.relu = relu;
   return run_chain(*p, P, (cudaStream_t)stream);
@@ -1044,6 +1097,10 @@ int tf_exec_phase(tf_plan *p, int phase, const float *in0, const float *in1, int
     p->launches = 1;
     return TF_OK;
   }
+  if (phase > 0 && gemm_march_usable(*p, in0, D, relu))
+    return phase == 1 ? run_gemm_march(*p, in0, in1, w_transposed, D, true, 0, p->march.n_phase1, false, (cudaStream_t)stream)
+                      : run_gemm_march(*p, in0, in1, w_transposed, D, false, p->march.n_phase1, p->march.n_items, true,
+                                       (cudaStream_t)stream);
   if (phase > 0 && p->chain == 0 && march_usable(*p, in0, D))
     return phase == 1 ? run_march(*p, in0, D, 0, p->march.n_phase1, false, (cudaStream_t)stream)
                       : run_march(*p, in0, D, p->march.n_phase1, p->march.n_items, true, (cudaStream_t)stream);
