@@ -132,7 +132,8 @@ typedef struct {
   int lattice_march;      /* SpMM-SpMM whose two operators are star stencils on one 3-D grid in natural order
                              (every nonzero names the row's own grid point or one of its six neighbours):
                              0 = run the plane-marching kernel, which keeps the intermediate in shared memory,
-                             <0 = never (general CSR path)                                               */
+                             <0 = never (general CSR path).  GeMM-SpMM plans on such an operator use the same
+                             kernel as the consumer of the tensor-core producer's rows (0) or the ticket executor (<0) */
   int exchange;           /* tf_multi_plan only: 0 = halo rows are written by the copy engines straight into the
                              neighbours' memory (CUDA IPC) where every rank is a process of its own on one host,
                              else ncclSend / ncclRecv; <0 = always ncclSend / ncclRecv (every rank must say the same) */
