@@ -143,6 +143,31 @@ def test_plane_march_shapes(torch_cuda, oracle, dims, n_cols):
         ref_plan.close()
 
 
+@pytest.mark.parametrize("dims,k,n_cols", [((18, 16, 9), 40, 64), ((34, 20, 6), 64, 112)])
+def test_gemm_spmm_marching_consumer(torch_cuda, oracle, dims, k, n_cols):
+    """GeMM-SpMM on a 3-D grid operator: the tensor-core producer's rows are consumed by the plane-marching kernel
+    (identity as first operator).  Against the oracle, and bit for bit against the ticket executor's consumer."""
+    torch = torch_cuda
+    a = synth.laplacian(dims)
+    n = len(a[0]) - 1
+    A = _csr(a)
+    b, w = synth.uniform(2, (n, k)), synth.uniform(3, (k, n_cols))
+    want, _ = oracle.gemm_spmm(a, b, w, oracle.inspect_fixed(a[0], a[1], 2, 64))
+    bd, wd = _dev(torch, b), _dev(torch, w)
+    got = {}
+    for name, lm in (("march", 0), ("ticket", -1)):
+        plan = api.Plan("gemm_spmm", A, k=k, n_cols=n_cols, lattice_march=lm)
+        assert (plan.info()["threads"] == 128) == (name == "march"), plan.info()
+        d = torch.full((n, n_cols), float("nan"), device="cuda")
+        for _ in range(2):
+            plan.gemm_spmm(bd, wd, d)
+        plan.status()
+        got[name] = d.cpu().numpy()
+        common.assert_close(got[name], want, f"GeMM-SpMM {name} consumer {dims}")
+        plan.close()
+    np.testing.assert_array_equal(got["march"], got["ticket"])
+
+
 def _nine_point(nx, ny):
     import scipy.sparse as sp
     x, y = np.meshgrid(np.arange(nx), np.arange(ny))
