@@ -11,6 +11,7 @@
 #ifndef TILE_FUSION_H
 #define TILE_FUSION_H
 
+#include <cstring>
 #include <map>
 #include <memory>
 #include <stdexcept>
@@ -28,6 +29,22 @@ struct CSRMatrix {
   float *Ax;
   CSRMatrix(int M_, int N_, int *Ap_, int *Ai_, float *Ax_) : M(M_), N(N_), Ap(Ap_), Ai(Ai_), Ax(Ax_) {}
   tf_csr view() const { return tf_csr{M, N, Ap, Ai, Ax}; }
+  // Sampled checksum of the matrix (size, up to 2048 evenly spaced column ids and values): the plan cache keys on it
+  // beside the array addresses, so that arrays refilled in place with another matrix get a new plan.  A change
+  // that touches none of the sampled entries is not seen: build a new CSRMatrix over new arrays for new values.
+  unsigned long long fingerprint() const {
+    unsigned long long h = 1469598103934665603ull;
+    auto mix = [&h](unsigned long long v) { h = (h ^ v) * 1099511628211ull; };
+    const long long nnz = Ap[M];
+    mix((unsigned long long)M); mix((unsigned long long)N); mix((unsigned long long)nnz);
+    const long long step = nnz > 2048 ? nnz / 2048 : 1;
+    for (long long j = 0; j < nnz; j += step) {
+      unsigned bits;
+      std::memcpy(&bits, &Ax[j], sizeof(bits));
+      mix(((unsigned long long)(unsigned)Ai[j] << 32) | bits);
+    }
+    return h;
+  }
 };
 
 struct Matrix {
@@ -67,7 +84,8 @@ class FusedSchedule {
 
   tf_plan *plan(int chain, const CSRMatrix &A, const CSRMatrix *B, int k, int n) const {
     if (!impl_) throw std::runtime_error("tile-fusion: empty schedule");
-    auto key = std::make_tuple(chain, (const void *)A.Ap, B ? (const void *)B->Ap : nullptr, k, n, mode);
+    auto key = std::make_tuple(chain, (const void *)A.Ap, B ? (const void *)B->Ap : nullptr, k, n, mode,
+                               A.fingerprint() ^ (B ? 31 * B->fingerprint() : 0ull));
     auto it = impl_->plans.find(key);
     if (it != impl_->plans.end()) return it->second;
     tf_plan_opts o{};
@@ -88,7 +106,7 @@ class FusedSchedule {
  private:
   struct Impl {
     tf_schedule *s;
-    std::map<std::tuple<int, const void *, const void *, int, int, int>, tf_plan *> plans;
+    std::map<std::tuple<int, const void *, const void *, int, int, int, unsigned long long>, tf_plan *> plans;
     explicit Impl(tf_schedule *s_) : s(s_) {}
     ~Impl() {
       for (auto &kv : plans) tf_plan_free(kv.second);

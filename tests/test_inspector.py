@@ -145,3 +145,16 @@ def test_executors_fail_loudly_without_a_gpu(built_lib):
     with pytest.raises(api.TileFusionError) as e:
         api.Plan("spmm_spmm", A, n_cols=32)
     assert e.value.code == _lib.TF_ERR_CUDA
+
+
+def test_fingerprint_sees_refilled_arrays():
+    """The README-level executors cache their plan per matrix; the key must change when the arrays are refilled
+    in place or when another matrix takes an old object's place."""
+    a = synth.laplacian((6, 5, 4))
+    A = api.CSRMatrix(len(a[0]) - 1, len(a[0]) - 1, *a)
+    f0 = A.fingerprint()
+    assert f0 == A.fingerprint()
+    A.Ax *= 2.0
+    assert A.fingerprint() != f0
+    b = synth.laplacian((6, 5, 4))
+    assert api.CSRMatrix(len(b[0]) - 1, len(b[0]) - 1, *b).fingerprint()[:5] == f0[:5]   # same matrix, other arrays

@@ -53,6 +53,16 @@ class CSRMatrix:
     def _c(self) -> _lib.Csr:
         return _lib.Csr(self.M, self.N, self.Ap.ctypes.data, self.Ai.ctypes.data, self.Ax.ctypes.data)
 
+    def fingerprint(self):
+        """Sampled checksum (size, up to 2048 evenly spaced column ids and values).  The plan cache of the
+        README-level executors keys on it beside the object, so that an object id reused by another matrix, or
+        arrays refilled in place, get a new plan.  A change that touches none of the sampled entries is not seen:
+        make a new CSRMatrix for new values."""
+        nnz = self.nnz
+        step = max(1, nnz // 2048)
+        return (self.M, self.N, nnz, int(self.Ai[::step].astype(np.int64).sum()),
+                self.Ax[::step].tobytes().__hash__(), self.Ap.ctypes.data, self.Ai.ctypes.data, self.Ax.ctypes.data)
+
 
 class Matrix:
     """Matrix(M, N, Data) -- README.md:38.  Data: numpy array (host) or CUDA torch tensor (device)."""
@@ -320,7 +330,7 @@ def spMMSpMMExecutor(A: CSRMatrix, B: CSRMatrix, C_: Matrix, D: Matrix, schedule
         raise ValueError("spMMSpMMExecutor: C and D must both be host or both be device data")
     m = _mode_for(schedule, mode)
     same = B is A
-    key = ("ss", id(A), id(B), C_.N, m, id(schedule) if m == MODE_SCHEDULE else 0)
+    key = ("ss", A.fingerprint(), B.fingerprint(), C_.N, m, id(schedule) if m == MODE_SCHEDULE else 0)
     plan = _cached_plan(key, lambda: Plan("spmm_spmm", A, B=None if same else B, n_cols=C_.N, mode=m,
                                           schedule=schedule if m == MODE_SCHEDULE else None))
     if C_.on_device:
@@ -341,7 +351,7 @@ def geMMSpMMExecutor(A: CSRMatrix, B: Matrix, C_: Matrix, D: Matrix, schedule: F
     if not (B.on_device == C_.on_device == D.on_device):
         raise ValueError("geMMSpMMExecutor: B, C and D must all be host or all be device data")
     m = _mode_for(schedule, mode)
-    key = ("gs", id(A), k, n, m, id(schedule) if m == MODE_SCHEDULE else 0)
+    key = ("gs", A.fingerprint(), k, n, m, id(schedule) if m == MODE_SCHEDULE else 0)
     plan = _cached_plan(key, lambda: Plan("gemm_spmm", A, k=k, n_cols=n, mode=m,
                                           schedule=schedule if m == MODE_SCHEDULE else None))
     if B.on_device:
@@ -355,7 +365,7 @@ def sddmmSpMMExecutor(A: CSRMatrix, Q: Matrix, K: Matrix, V: Matrix, D: Matrix):
     """D = (A .* (Q K^T)) V.  The reference has the SDDMM half only (codegen/triton/sddmm.py:173-184)."""
     if Q.N != K.N or Q.M != A.M or K.M != A.N or V.M != A.N or D.M != A.M or D.N != V.N:
         raise ValueError("sddmmSpMMExecutor: shapes do not chain")
-    key = ("sd", id(A), Q.N, V.N)
+    key = ("sd", A.fingerprint(), Q.N, V.N)
     plan = _cached_plan(key, lambda: Plan("sddmm_spmm", A, k=Q.N, n_cols=V.N))
     if Q.on_device:
         plan.sddmm_spmm(Q.Data, K.Data, V.Data, D.Data)
