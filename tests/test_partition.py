@@ -123,3 +123,20 @@ def test_halo_exchange_two_ranks_gloo():
     want = A @ (synth.uniform(2, (n, 8)).astype(np.float64) @ synth.uniform(3, (8, nc)).astype(np.float64))
     got = np.concatenate([ret[g][1] for g in range(world)])
     np.testing.assert_allclose(got, want, rtol=1e-12, atol=1e-12)
+
+
+def test_multi_entry_points_reject_bad_arguments(built_lib):
+    """The multi-GPU entry points answer with a status, not a crash, when handed nothing (no GPU, no NCCL needed)."""
+    import ctypes as C
+
+    from tile_fusion_b200 import _lib
+    L = _lib.lib()
+    ms = (C.c_float * 5)()
+    assert L.tf_multi_trace(None, 1, ms) == _lib.TF_ERR_ARG
+    assert L.tf_multi_status(None, None) == _lib.TF_ERR_ARG
+    assert L.tf_multi_exec(None, None, None, 0, 0, None, None) == _lib.TF_ERR_ARG
+    out = C.c_void_p()
+    assert L.tf_comm_create(None, 2, 0, C.byref(out)) == _lib.TF_ERR_ARG
+    assert L.tf_comm_from_nccl(None, 2, 0, C.byref(out)) == _lib.TF_ERR_ARG
+    assert L.tf_multi_plan(None, 0, 0, 10, None, None, None, 0, 8, None, C.byref(out)) == _lib.TF_ERR_ARG
+    assert b"null" in L.tf_last_error() or b"bad" in L.tf_last_error()
