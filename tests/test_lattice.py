@@ -100,3 +100,61 @@ def test_items_cover_every_output_once(built_lib, dims, n_cols, ctas):
     assert max(free) <= equal
     if dims == (128, 128, 128):
         assert max(free) == 3 * 132 + 68       # three rounds of whole columns, then 296 pieces of at most 64 planes
+
+
+def _apply_planes(r, c_planes, z):
+    """One plane of (operator x operand) from the class table: out[y, x, :] = sum over the seven stencil points of
+    dict[class(x, y, z)][k] * operand(point k), operand planes outside [0, nz) taken as zero."""
+    nx, ny, nz = r["nx"], r["ny"], r["nz"]
+    w = r["patch_cls"][z]
+    ys, xs = np.meshgrid(np.arange(ny), np.arange(nx), indexing="ij")
+    cls = (w[ys // 2, xs // 2] >> (8 * (2 * (ys & 1) + (xs & 1)))) & 255
+    coef = r["dict"][cls].astype(np.float64)               # [ny, nx, 8]
+    zero = np.zeros_like(c_planes[0])
+    cur = c_planes[z]
+    below = c_planes[z - 1] if z - 1 >= 0 else zero
+    above = c_planes[z + 1] if z + 1 < nz else zero
+    pad = np.pad(cur, ((1, 1), (1, 1), (0, 0)))
+    parts = [below, pad[:-2, 1:-1], pad[1:-1, :-2], cur, pad[1:-1, 2:], pad[2:, 1:-1], above]
+    return sum(coef[:, :, k, None] * p for k, p in enumerate(parts))
+
+
+@pytest.mark.parametrize("dims,n_cols,ctas", [((8, 6, 10), 24, 5), ((18, 10, 7), 16, 296)])
+def test_marching_recurrence_over_the_work_list(built_lib, dims, n_cols, ctas):
+    """The plane-marching algorithm replayed on the host from what the library hands its kernel -- class words,
+    dictionary, work items: every item marches its planes with the kernel's lead-in rule (two planes in front of the
+    first output plane, none below plane 0), builds T one plane ahead of D and writes its tile's rows of D.  The
+    union of the items must be A (A C)."""
+    import scipy.sparse as sp
+    a = synth.laplacian(dims)
+    n = len(a[0]) - 1
+    rows = np.repeat(np.arange(n), np.diff(a[0]))
+    ax = (a[2] * (1.0 + 0.25 * (rows % 3))).astype(np.float32)
+    r = api.lattice_preview(_csr((a[0], a[1], ax)), n_cols=n_cols, ctas=ctas)
+    nx, ny, nz = dims
+    c = synth.uniform(5, (n, n_cols)).astype(np.float64)
+    c_planes = c.reshape(nz, ny, nx, n_cols)
+    A = sp.csr_matrix((ax.astype(np.float64), a[1], a[0]), shape=(n, n))
+    want = (A @ (A @ c)).reshape(nz, ny, nx, n_cols)
+    got = np.full_like(want, np.nan)
+    for x0, y0, zs, ze, c0, _ in r["items"]:
+        cols = slice(c0, min(c0 + 16, n_cols))
+        kfirst = zs - (0 if zs == 0 else 2)
+        t_planes = {}
+        for k in range(kfirst, ze + 2):          # plane C(k) arrives
+            # T(k-1) is complete once C(k) is there; D(k-2) once T(k-1) is
+            if 0 <= k - 1 < nz:
+                t_planes[k - 1] = _apply_planes(r, c_planes, k - 1)[:, :, cols]
+            z = k - 2
+            if zs <= z < ze:
+                t_full = np.zeros((nz, ny, nx, cols.stop - cols.start))
+                for q in (z - 1, z, z + 1):
+                    if 0 <= q < nz:
+                        assert q in t_planes, (zs, ze, k, q)   # the lead-in planes were enough
+                        t_full[q] = t_planes[q]
+                d = _apply_planes(r, t_full, z)
+                ty, tx = slice(y0, min(y0 + 8, ny)), slice(x0, min(x0 + 16, nx))
+                assert np.all(np.isnan(got[z, ty, tx, cols]))     # every output is written once
+                got[z, ty, tx, cols] = d[ty, tx]
+    assert not np.isnan(got).any()
+    np.testing.assert_allclose(got, want, rtol=1e-12, atol=1e-12)
